@@ -1,0 +1,116 @@
+/* C ABI of libb200hybrid.so: the operators of hybrid decoders (latent attention with a sink, decayed linear attention,
+ * routed experts, grouped RMS norm, short causal convolution, depth-weighted residual history) for sm_100a.
+ *
+ * Conventions shared by all entries: raw device pointers, sizes as int, `stream` a cudaStream_t, return 0 on success, a
+ * negative b200h_status for refused arguments, a positive cudaError_t for a failed launch; b200h_last_error() says why.
+ * `dtype` is the type T of projection outputs and weights: B200H_BF16 or B200H_F32.  The residual stream, norm weights,
+ * router weights, recurrent state and everything named `float` below are 32-bit floats whatever T is.
+ * A step has n rows; row t belongs to batch entry tok_seq[t], at position tok_pos[t]; cu_q[s] is entry s's first row. */
+#ifndef B200_HYBRID_H
+#define B200_HYBRID_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+#define B200H_API extern "C" __attribute__((visibility("default")))
+#else
+#define B200H_API
+#endif
+
+#define B200H_BF16 1
+#define B200H_F32 2
+#define B200H_MAX_TAPS 16
+
+enum b200h_status { B200H_ERR_INVALID_ARG = -1, B200H_ERR_UNSUPPORTED = -2 };
+
+/* Rotation of interleaved pairs (2i, 2i+1), i < pairs, by the angle position * freqs[i]; cos and sin times magnitude.
+ * freqs: `pairs` doubles in device memory. */
+typedef struct b200h_rotary {
+    const void* freqs;
+    int pairs;
+    float magnitude;
+} b200h_rotary;
+
+/* One latent-attention layer of one step.
+ * Cache entry of a position inside its page (page address + layer_off): the normed latent as T at [pos % block_len][kv_rank],
+ * and, rot_off bytes further, the rotated shared key part as float at [pos % block_len][rot_dim]. */
+typedef struct b200h_latent_args {
+    int n, heads, dim, rot_dim, vdim, kv_rank, q_rank, block_len;
+    float scale, eps;
+    b200h_rotary rot;
+    const void* dq;          /* T [n, ld_dq]: query latent before its norm (q_rank columns) */
+    int64_t ld_dq;
+    const void* dkv;         /* T [n, ld_dkv]: kv_rank latent columns, then rot_dim shared key columns */
+    int64_t ld_dkv;
+    const void* q_norm;      /* float [q_rank] */
+    const void* kv_norm;     /* float [kv_rank] */
+    void* cq;                /* T [n, q_rank]: out of b200h_latent_prep */
+    const void* q;           /* T [n, ld_q]: per head dim plain then rot_dim rotated columns */
+    int64_t ld_q;
+    const void* uk;          /* T [heads * dim, kv_rank] */
+    const void* uv;          /* T [heads * vdim, kv_rank] */
+    const void* sink;        /* float [heads] */
+    const void* gate;        /* T [n, ld_gate]: heads * vdim columns, before the sigmoid */
+    int64_t ld_gate;
+    void* q_lat;             /* float [n, heads, kv_rank] scratch */
+    void* q_rot;             /* float [n, heads, rot_dim] scratch */
+    void* o_lat;             /* float [n, heads, kv_rank] scratch */
+    void* y;                 /* T [n, heads * vdim]: gated heads, the output projection's input */
+    const void* tok_seq;     /* int [n] */
+    const void* tok_pos;     /* int [n] */
+    const void* block_ptrs;  /* int64: page addresses, entry s's pages from cu_blocks[s] */
+    const void* cu_blocks;   /* int [batch + 1] */
+    int64_t layer_off, rot_off;
+    int dtype;
+    void* stream;
+} b200h_latent_args;
+
+B200H_API const char* b200h_last_error(void);
+
+/* out[t] = table[tokens[t]] * scale (float). */
+B200H_API int b200h_embed(const void* tokens, const void* table, float scale, void* out, int n, int width, int dtype, void* stream);
+
+/* out[t] = x[t] + sum_j w[:, j] * x[t - taps + 1 + j] as T, x float [n, width], w float [width, taps]; rows before an entry's first
+ * come from its state (float [taps - 1, width] at state + seq_slot[s] * slot_stride), which is then advanced by the step. */
+B200H_API int b200h_causal_conv(const void* x, const void* w, void* state, int64_t slot_stride, const void* tok_seq, const void* cu_q,
+                                const void* seq_slot, void* out, int n, int batch, int width, int taps, int dtype, void* stream);
+
+/* x[t] += w * (sum_p m[t, p]) / rms per group; m is T (or float when m_is_f32) [n, parts, width]; x_t (optional): x as T. */
+B200H_API int b200h_residual_group_norm(void* x, const void* m, int m_is_f32, int parts, const void* w, int n, int width, int groups,
+                                        float eps, void* x_t, int dtype, void* stream);
+
+/* out[r] = w * x[rows[r]] / rms per group as T (rows NULL: the first `count` rows). */
+B200H_API int b200h_group_norm_rows(const void* x, const void* rows, const void* w, int count, int width, int groups, float eps, void* out,
+                                    int dtype, void* stream);
+
+/* hist[terms - 1] <- x; x <- sum_j coef[j] * hist[j] (j < terms); hist[j] starts hist_stride floats after hist[j - 1]. */
+B200H_API int b200h_depth_mix(void* x, void* hist, int64_t hist_stride, const void* coef, int terms, int64_t count, void* stream);
+
+/* Norm of both latents, rotation of the shared key part, cache store (fills cq). */
+B200H_API int b200h_latent_prep(const b200h_latent_args* args);
+/* Queries into latent coordinates, causal attention over the cache with the sink, value expansion and output gate (fills y). */
+B200H_API int b200h_latent_attention(const b200h_latent_args* args);
+
+/* Per head S <- decay S + silu(k) silu(v)^T, out = S^T silu(q) (float [n, heads, vdim]); q, k, v are T with row stride ld;
+ * state float [heads, vdim, dim] at state + seq_slot[s] * slot_stride, read and advanced. */
+B200H_API int b200h_decay_attention(const void* q, const void* k, const void* v, int64_t ld, const void* decay, void* state,
+                                    int64_t slot_stride, const void* cu_q, const void* seq_slot, int batch, int heads, int dim, int vdim,
+                                    void* out, int dtype, void* stream);
+
+/* y[t] = o[t] / rms(o[t]) * w * sigmoid(gate[t]) as T over `count` columns. */
+B200H_API int b200h_gated_rms(const void* o, const void* w, const void* gate, int64_t ld_gate, int n, int count, float eps, void* y,
+                              int dtype, void* stream);
+
+/* softmax(router x) over all experts; ids / wts [n, top]: the top largest and their scores. */
+B200H_API int b200h_route(const void* x, const void* router, int n, int width, int experts, int top, void* ids, void* wts, void* stream);
+
+/* out[t, k] = wts[t, k] * down_e (silu(gate_e x[t]) * (up_e x[t])), e = ids[t, k]; gate, up T [experts, ff, width], down T [experts, width, ff];
+ * out float [n, top, width]. */
+B200H_API int b200h_experts(const void* x, const void* gate, const void* up, const void* down, const void* ids, const void* wts, int n,
+                            int width, int ff, int top, void* out, int dtype, void* stream);
+
+/* out[r] = index of the largest of logits[r, :vocab] (float, row stride ld; ties: the lowest index). */
+B200H_API int b200h_argmax(const void* logits, int64_t ld, int rows, int vocab, void* out, void* stream);
+
+#endif

@@ -1,0 +1,64 @@
+"""ctypes binding of libb200hybrid.so (include/b200_hybrid.h): the operators of hybrid decoders.  Built on first use from
+lmdeploy_b200/csrc/hybrid (one translation unit, seconds with nvcc); there is no fallback when it cannot be built or loaded."""
+import ctypes as C
+import os
+
+from ._lib import B200LibraryError
+
+BF16, F32 = 1, 2
+MAX_TAPS = 16
+
+
+class Rotary(C.Structure):
+    _fields_ = [("freqs", C.c_void_p), ("pairs", C.c_int), ("magnitude", C.c_float)]
+
+
+class LatentArgs(C.Structure):
+    """b200h_latent_args."""
+    _fields_ = [
+        ("n", C.c_int), ("heads", C.c_int), ("dim", C.c_int), ("rot_dim", C.c_int), ("vdim", C.c_int), ("kv_rank", C.c_int),
+        ("q_rank", C.c_int), ("block_len", C.c_int), ("scale", C.c_float), ("eps", C.c_float), ("rot", Rotary),
+        ("dq", C.c_void_p), ("ld_dq", C.c_int64), ("dkv", C.c_void_p), ("ld_dkv", C.c_int64),
+        ("q_norm", C.c_void_p), ("kv_norm", C.c_void_p), ("cq", C.c_void_p),
+        ("q", C.c_void_p), ("ld_q", C.c_int64), ("uk", C.c_void_p), ("uv", C.c_void_p), ("sink", C.c_void_p),
+        ("gate", C.c_void_p), ("ld_gate", C.c_int64),
+        ("q_lat", C.c_void_p), ("q_rot", C.c_void_p), ("o_lat", C.c_void_p), ("y", C.c_void_p),
+        ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("block_ptrs", C.c_void_p), ("cu_blocks", C.c_void_p),
+        ("layer_off", C.c_int64), ("rot_off", C.c_int64), ("dtype", C.c_int), ("stream", C.c_void_p),
+    ]
+
+
+_lib = None
+P, I, L64, F = C.c_void_p, C.c_int, C.c_int64, C.c_float
+
+
+def load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    from . import build
+    path = os.environ.get("B200_HYBRID_LIB_PATH") or build.build_hybrid()
+    try:
+        lib = C.CDLL(path)
+    except OSError as e:  # pragma: no cover
+        raise B200LibraryError(f"cannot load {path}: {e}") from e
+    lib.b200h_last_error.restype = C.c_char_p
+    lib.b200h_embed.argtypes = [P, P, F, P, I, I, I, P]
+    lib.b200h_causal_conv.argtypes = [P, P, P, L64, P, P, P, P, I, I, I, I, I, P]
+    lib.b200h_residual_group_norm.argtypes = [P, P, I, I, P, I, I, I, F, P, I, P]
+    lib.b200h_group_norm_rows.argtypes = [P, P, P, I, I, I, F, P, I, P]
+    lib.b200h_depth_mix.argtypes = [P, P, L64, P, I, L64, P]
+    lib.b200h_latent_prep.argtypes = [C.POINTER(LatentArgs)]
+    lib.b200h_latent_attention.argtypes = [C.POINTER(LatentArgs)]
+    lib.b200h_decay_attention.argtypes = [P, P, P, L64, P, P, L64, P, P, I, I, I, I, P, I, P]
+    lib.b200h_gated_rms.argtypes = [P, P, P, L64, I, I, F, P, I, P]
+    lib.b200h_route.argtypes = [P, P, I, I, I, I, P, P, P]
+    lib.b200h_experts.argtypes = [P, P, P, P, P, P, I, I, I, I, P, I, P]
+    lib.b200h_argmax.argtypes = [P, L64, I, I, P, P]
+    _lib = lib
+    return lib
+
+
+def check(rc, what=""):
+    if rc != 0:
+        raise B200LibraryError(f"{what} failed (code {rc}): {load().b200h_last_error().decode()}")

@@ -65,5 +65,28 @@ def build(force=False, verbose=False):
     return LIB
 
 
+HYBRID_SRC = os.path.join(CSRC, "hybrid", "hybrid_ops.cu")
+HYBRID_LIB = os.path.join(LIBDIR, "libb200hybrid.so")
+
+
+def build_hybrid(force=False):
+    """lmdeploy_b200/csrc/hybrid/hybrid_ops.cu -> lmdeploy_b200/lib/libb200hybrid.so (the operators of hybrid decoders; one
+    translation unit, independent of libb200tm.so so that serving such a model compiles nothing else).  Rebuilt when the
+    source or its header is newer; concurrent builders write to a private name and rename."""
+    hdr = os.path.join(REPO, "include", "b200_hybrid.h")
+    if not force and os.path.exists(HYBRID_LIB) and \
+            os.path.getmtime(HYBRID_LIB) >= max(os.path.getmtime(HYBRID_SRC), os.path.getmtime(hdr)):
+        return HYBRID_LIB
+    os.makedirs(LIBDIR, exist_ok=True)
+    tmp = f"{HYBRID_LIB}.{os.getpid()}.tmp"
+    cmd = [NVCC, *FLAGS, "-shared", "-o", tmp, HYBRID_SRC, "-lcudart"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, HYBRID_LIB)
+    return HYBRID_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True))
+    print(build_hybrid(force="--force" in sys.argv))

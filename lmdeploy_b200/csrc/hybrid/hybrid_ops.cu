@@ -1,0 +1,689 @@
+// Operators of hybrid decoders (latent attention with a sink, decayed linear attention, routed experts, grouped RMS norm,
+// short causal convolution, depth-weighted residual history) behind a C ABI of their own: libb200hybrid.so.
+//
+// Number formats.  T is the activation / weight type of the matrix products (float or bf16).  Everything the designs want in
+// 32 bits is float here whatever T is: the residual stream and its history, every norm, rotary angles (double), attention
+// scores and the online softmax, recurrent state, router scores.  Kernels read T only where a projection wrote it.
+//
+// Token addressing.  A step carries `n` rows; row t belongs to sequence tok_seq[t] of the batch and sits at position
+// tok_pos[t] of that sequence.  cu_q[s] is the first row of sequence s (rows of a sequence are consecutive and in order).
+// Paged cache: block_ptrs[cu_blocks[s] + p / block_len] is the address of the page that holds position p of sequence s;
+// a layer's region starts layer_off bytes into the page.  Recurrent state: state + seq_slot[s] * slot_stride + layer offset.
+#include "../../../include/b200_hybrid.h"
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200h {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Sum over the block; every thread gets the result.  blockDim.x is a multiple of 32, at most 1024.
+__device__ __forceinline__ float block_sum(float v, float* red)
+{
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();                       // red may still be read from an earlier call
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = 0.f;
+    for (int i = 0; i < nw; ++i) r += red[i];
+    return r;
+}
+
+// ------------------------------------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float scale, float* __restrict__ out,
+                             int width)
+{
+    const int t = blockIdx.x;
+    const T* row = table + (size_t)tokens[t] * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)t * width + i] = to_f(row[i]) * scale;
+}
+
+// ------------------------------------------------------------------------------------------------ short causal convolution
+// out[t] = x[t] + sum_j w[:, j] * x[t - taps + 1 + j]; rows before the step's first come from the sequence's state
+// (its last taps-1 inputs, oldest first), zeros at a sequence's start because a fresh slot is zeroed.
+template <typename T>
+__global__ void conv_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ state,
+                            int64_t slot_stride, const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
+                            const int* __restrict__ seq_slot, T* __restrict__ out, int width, int taps)
+{
+    const int t = blockIdx.x, s = tok_seq[t], first = cu_q[s], local = t - first;
+    const float* st = state + (int64_t)seq_slot[s] * slot_stride;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = x[(size_t)t * width + c];
+        for (int j = 0; j < taps; ++j) {
+            const int src = local - (taps - 1) + j;
+            const float v = src >= 0 ? x[(size_t)(first + src) * width + c] : st[(size_t)(src + taps - 1) * width + c];
+            acc += w[c * taps + j] * v;
+        }
+        out[(size_t)t * width + c] = from_f<T>(acc);
+    }
+}
+
+// The state after the step: the last taps-1 inputs of (old state ++ this step's rows).  One thread owns a (sequence, channel)
+// pair, reads all it needs and then writes, so a step shorter than taps-1 shifts the state correctly.
+__global__ void conv_state_kernel(const float* __restrict__ x, float* __restrict__ state, int64_t slot_stride,
+                                  const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int width, int taps)
+{
+    const int s = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int first = cu_q[s], n = cu_q[s + 1] - first;
+    if (c >= width || n == 0) return;
+    float* st = state + (int64_t)seq_slot[s] * slot_stride;
+    float keep[B200H_MAX_TAPS];
+    for (int k = 0; k < taps - 1; ++k) {
+        const int src = n + k - (taps - 1);
+        keep[k] = src >= 0 ? x[(size_t)(first + src) * width + c] : st[(size_t)(src + taps - 1) * width + c];
+    }
+    for (int k = 0; k < taps - 1; ++k) st[(size_t)k * width + c] = keep[k];
+}
+
+// ------------------------------------------------------------------------------------------------ grouped RMS norm
+// x[t] += w * unit_rms_per_group(sum_p m[t, p]); optionally also writes x as T (the next projection's input).
+template <typename TI, typename T>
+__global__ void residual_group_norm_kernel(float* __restrict__ x, const TI* __restrict__ m, int parts, const float* __restrict__ w,
+                                           int width, int groups, float eps, T* __restrict__ x_t)
+{
+    __shared__ float red[32];
+    const int t = blockIdx.x, g = blockIdx.y, gw = width / groups;
+    const TI* mt = m + (size_t)t * parts * width + g * gw;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gw; i += blockDim.x) {
+        float v = 0.f;
+        for (int p = 0; p < parts; ++p) v += to_f(mt[(size_t)p * width + i]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)gw + eps);
+    for (int i = threadIdx.x; i < gw; i += blockDim.x) {
+        float v = 0.f;
+        for (int p = 0; p < parts; ++p) v += to_f(mt[(size_t)p * width + i]);
+        const size_t at = (size_t)t * width + g * gw + i;
+        const float y = x[at] + v * r * w[g * gw + i];
+        x[at] = y;
+        if (x_t) x_t[at] = from_f<T>(y);
+    }
+}
+
+// out[r] = w * unit_rms_per_group(x[rows[r]]) as T (rows == nullptr: row r).
+template <typename T>
+__global__ void group_norm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                                       int width, int groups, float eps, T* __restrict__ out)
+{
+    __shared__ float red[32];
+    const int r = blockIdx.x, g = blockIdx.y, gw = width / groups;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * width + g * gw;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gw; i += blockDim.x) ss += xr[i] * xr[i];
+    ss = block_sum(ss, red);
+    const float k = 1.0f / sqrtf(ss / (float)gw + eps);
+    for (int i = threadIdx.x; i < gw; i += blockDim.x) out[(size_t)r * width + g * gw + i] = from_f<T>(xr[i] * k * w[g * gw + i]);
+}
+
+// ------------------------------------------------------------------------------------------------ depth-weighted history
+// hist[terms-1] <- x (the layer's result); x <- sum_j coef[j] * hist[j], j ascending.
+__global__ void depth_mix_kernel(float* __restrict__ x, float* __restrict__ hist, int64_t hist_stride, const float* __restrict__ coef,
+                                 int terms, int64_t count)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const float last = x[i];
+    hist[(int64_t)(terms - 1) * hist_stride + i] = last;
+    float acc = 0.f;
+    for (int j = 0; j < terms - 1; ++j) acc += coef[j] * hist[(int64_t)j * hist_stride + i];
+    x[i] = acc + coef[terms - 1] * last;
+}
+
+// ------------------------------------------------------------------------------------------------ latent attention
+struct Rotary {
+    const double* freqs;      // angle per position of pair i, i < pairs
+    int pairs;                // rotated pairs; dimensions from 2 * pairs on pass unchanged
+    float magnitude;          // factor on cos and sin
+};
+
+__device__ __forceinline__ void rotate_pair(float u, float v, int pos, double f, float mag, float& ru, float& rv)
+{
+    double sn, cs;
+    sincos((double)pos * f, &sn, &cs);
+    const float c = (float)cs * mag, s = (float)sn * mag;
+    ru = u * c - v * s;
+    rv = v * c + u * s;
+}
+
+// One block per row: the query latent is normed (-> cq as T), the key/value latent is normed and written to the row's cache
+// entry as T, the shared rotated key part is rotated and written to the cache as float.
+template <typename T>
+__global__ void latent_prep_kernel(const T* __restrict__ dq, int64_t ld_dq, int q_rank, const float* __restrict__ wq,
+                                   const T* __restrict__ dkv, int64_t ld_dkv, int kv_rank, int rot_dim, const float* __restrict__ wkv,
+                                   float eps, Rotary rot, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                   const int64_t* __restrict__ block_ptrs, const int* __restrict__ cu_blocks, int64_t layer_off,
+                                   int block_len, int64_t rot_off, T* __restrict__ cq)
+{
+    __shared__ float red[32];
+    const int t = blockIdx.x, s = tok_seq[t], pos = tok_pos[t];
+    const T* q = dq + (size_t)t * ld_dq;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) { const float v = to_f(q[i]); ss += v * v; }
+    ss = block_sum(ss, red);
+    float r = 1.0f / sqrtf(ss / (float)q_rank + eps);
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[(size_t)t * q_rank + i] = from_f<T>(to_f(q[i]) * r * wq[i]);
+
+    const T* kv = dkv + (size_t)t * ld_dkv;
+    char* page = reinterpret_cast<char*>(block_ptrs[cu_blocks[s] + pos / block_len]) + layer_off;
+    const int at = pos % block_len;
+    T* c_dst = reinterpret_cast<T*>(page) + (size_t)at * kv_rank;
+    float* r_dst = reinterpret_cast<float*>(page + rot_off) + (size_t)at * rot_dim;
+    ss = 0.f;
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) { const float v = to_f(kv[i]); ss += v * v; }
+    ss = block_sum(ss, red);
+    r = 1.0f / sqrtf(ss / (float)kv_rank + eps);
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) c_dst[i] = from_f<T>(to_f(kv[i]) * r * wkv[i]);
+    const T* kr = kv + kv_rank;
+    for (int i = threadIdx.x; i < rot.pairs; i += blockDim.x)
+        rotate_pair(to_f(kr[2 * i]), to_f(kr[2 * i + 1]), pos, rot.freqs[i], rot.magnitude, r_dst[2 * i], r_dst[2 * i + 1]);
+    for (int i = 2 * rot.pairs + threadIdx.x; i < rot_dim; i += blockDim.x) r_dst[i] = to_f(kr[i]);
+}
+
+// Queries in the latent's coordinates: q_lat[t, h, :] = scale * uk_h^T q_plain[t, h, :] (so that q_lat . c == q_plain . (uk_h c)),
+// q_rot[t, h, :] = scale * rotated part.  One block per (row, head).
+template <typename T>
+__global__ void latent_query_kernel(const T* __restrict__ q, int64_t ld_q, const T* __restrict__ uk, int heads, int dim, int rot_dim,
+                                    int kv_rank, float scale, Rotary rot, const int* __restrict__ tok_pos,
+                                    float* __restrict__ q_lat, float* __restrict__ q_rot)
+{
+    extern __shared__ float sm[];
+    const int t = blockIdx.x, h = blockIdx.y, pos = tok_pos[t];
+    const T* qh = q + (size_t)t * ld_q + (size_t)h * (dim + rot_dim);
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) sm[d] = to_f(qh[d]);
+    __syncthreads();
+    const T* ukh = uk + (size_t)h * dim * kv_rank;
+    float* ql = q_lat + ((size_t)t * heads + h) * kv_rank;
+    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
+        float acc = 0.f;
+        for (int d = 0; d < dim; ++d) acc = fmaf(sm[d], to_f(ukh[(size_t)d * kv_rank + c]), acc);
+        ql[c] = acc * scale;
+    }
+    const T* qr = qh + dim;
+    float* out = q_rot + ((size_t)t * heads + h) * rot_dim;
+    for (int i = threadIdx.x; i < rot.pairs; i += blockDim.x) {
+        float a, b;
+        rotate_pair(to_f(qr[2 * i]), to_f(qr[2 * i + 1]), pos, rot.freqs[i], rot.magnitude, a, b);
+        out[2 * i] = a * scale;
+        out[2 * i + 1] = b * scale;
+    }
+    for (int i = 2 * rot.pairs + threadIdx.x; i < rot_dim; i += blockDim.x) out[i] = to_f(qr[i]) * scale;
+}
+
+// Causal attention of one (row, head) per warp over the cached latents: score_j = q_lat . c_j + q_rot . kr_j, online softmax
+// that starts from the sink (a term exp(sink_h) in the denominator with no value), o_lat = sum_j w_j c_j.  Lane l owns the
+// latent coordinates l, l + 32, ...; a key's latent is loaded once and used for the score and for the weighted sum.
+template <typename T, int NC, int NR>
+__global__ void latent_attention_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot, const float* __restrict__ sink,
+                                        int heads, int kv_rank, int rot_dim, const int* __restrict__ tok_seq,
+                                        const int* __restrict__ tok_pos, const int64_t* __restrict__ block_ptrs,
+                                        const int* __restrict__ cu_blocks, int64_t layer_off, int block_len, int64_t rot_off,
+                                        float* __restrict__ o_lat)
+{
+    const int t = blockIdx.x, h = blockIdx.y * blockDim.y + threadIdx.y, lane = threadIdx.x;
+    if (h >= heads) return;
+    const int s = tok_seq[t], pos = tok_pos[t];
+    float ql[NC], qr[NR], acc[NC];
+    const float* qlp = q_lat + ((size_t)t * heads + h) * kv_rank;
+    const float* qrp = q_rot + ((size_t)t * heads + h) * rot_dim;
+#pragma unroll
+    for (int i = 0; i < NC; ++i) { const int c = i * 32 + lane; ql[i] = c < kv_rank ? qlp[c] : 0.f; acc[i] = 0.f; }
+#pragma unroll
+    for (int i = 0; i < NR; ++i) { const int c = i * 32 + lane; qr[i] = c < rot_dim ? qrp[c] : 0.f; }
+    float m = sink[h], l = 1.0f;
+    const int64_t* pages = block_ptrs + cu_blocks[s];
+    for (int j0 = 0; j0 <= pos; j0 += block_len) {
+        const char* page = reinterpret_cast<const char*>(pages[j0 / block_len]) + layer_off;
+        const T* cp = reinterpret_cast<const T*>(page);
+        const float* rp = reinterpret_cast<const float*>(page + rot_off);
+        const int cnt = min(block_len, pos + 1 - j0);
+        for (int j = 0; j < cnt; ++j) {
+            float cv[NC], part = 0.f;
+#pragma unroll
+            for (int i = 0; i < NC; ++i) {
+                const int c = i * 32 + lane;
+                cv[i] = c < kv_rank ? to_f(cp[(size_t)j * kv_rank + c]) : 0.f;
+                part = fmaf(ql[i], cv[i], part);
+            }
+#pragma unroll
+            for (int i = 0; i < NR; ++i) {
+                const int c = i * 32 + lane;
+                if (c < rot_dim) part = fmaf(qr[i], rp[(size_t)j * rot_dim + c], part);
+            }
+            const float sc = warp_sum(part);
+            const float mn = fmaxf(m, sc);
+            const float alpha = expf(m - mn), p = expf(sc - mn);
+            l = l * alpha + p;
+#pragma unroll
+            for (int i = 0; i < NC; ++i) acc[i] = acc[i] * alpha + p * cv[i];
+            m = mn;
+        }
+    }
+    const float inv = 1.0f / l;
+    float* out = o_lat + ((size_t)t * heads + h) * kv_rank;
+#pragma unroll
+    for (int i = 0; i < NC; ++i) { const int c = i * 32 + lane; if (c < kv_rank) out[c] = acc[i] * inv; }
+}
+
+// y[t, h*vdim + v] = (uv_h o_lat[t, h])[v] * sigmoid(gate[t, h*vdim + v]) as T.  One block per (row, head), a warp per value row.
+template <typename T>
+__global__ void latent_out_kernel(const float* __restrict__ o_lat, const T* __restrict__ uv, const T* __restrict__ gate, int64_t ld_gate,
+                                  int heads, int vdim, int kv_rank, T* __restrict__ y)
+{
+    extern __shared__ float sm[];
+    const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float* ol = o_lat + ((size_t)t * heads + h) * kv_rank;
+    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) sm[c] = ol[c];
+    __syncthreads();
+    for (int v = warp; v < vdim; v += nw) {
+        const T* row = uv + ((size_t)h * vdim + v) * kv_rank;
+        float part = 0.f;
+        for (int c = lane; c < kv_rank; c += 32) part = fmaf(to_f(row[c]), sm[c], part);
+        part = warp_sum(part);
+        if (lane == 0) {
+            const size_t col = (size_t)h * vdim + v;
+            y[(size_t)t * heads * vdim + col] = from_f<T>(part * sigmoid_f(to_f(gate[(size_t)t * ld_gate + col])));
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ decayed linear attention
+// Per head S <- decay * S + k v^T, o = S^T q with q, k, v = silu(projection).  The columns of S are independent, so one warp
+// owns one (sequence, head, value column): lane l keeps rows l, l + 32, ... of that column in registers and walks the
+// sequence's rows of this step in order.  State layout per head: [vdim][dim] floats.
+template <typename T, int NW>
+__global__ void decay_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int64_t ld,
+                                  const float* __restrict__ decay, float* __restrict__ state, int64_t slot_stride,
+                                  const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int dim, int vdim,
+                                  float* __restrict__ out)
+{
+    const int col = blockIdx.x * blockDim.y + threadIdx.y, h = blockIdx.y, s = blockIdx.z, lane = threadIdx.x;
+    if (col >= vdim) return;
+    const int first = cu_q[s], last = cu_q[s + 1];
+    if (first == last) return;
+    float* sp = state + (int64_t)seq_slot[s] * slot_stride + ((size_t)h * vdim + col) * dim;
+    float st[NW];
+#pragma unroll
+    for (int i = 0; i < NW; ++i) { const int d = i * 32 + lane; st[i] = d < dim ? sp[d] : 0.f; }
+    const float lam = decay[h];
+    for (int t = first; t < last; ++t) {
+        const T* qt = q + (size_t)t * ld + (size_t)h * dim;
+        const T* kt = k + (size_t)t * ld + (size_t)h * dim;
+        const float vv = silu_f(to_f(v[(size_t)t * ld + (size_t)h * vdim + col]));
+        float part = 0.f;
+#pragma unroll
+        for (int i = 0; i < NW; ++i) {
+            const int d = i * 32 + lane;
+            if (d < dim) {
+                st[i] = fmaf(lam, st[i], silu_f(to_f(kt[d])) * vv);
+                part = fmaf(st[i], silu_f(to_f(qt[d])), part);
+            }
+        }
+        part = warp_sum(part);
+        if (lane == 0) out[((size_t)t * heads + h) * vdim + col] = part;
+    }
+#pragma unroll
+    for (int i = 0; i < NW; ++i) { const int d = i * 32 + lane; if (d < dim) sp[d] = st[i]; }
+}
+
+// y[t] = unit_rms(o[t]) * w * sigmoid(gate[t]) as T over the concatenated heads.
+template <typename T>
+__global__ void gated_rms_kernel(const float* __restrict__ o, const float* __restrict__ w, const T* __restrict__ gate, int64_t ld_gate,
+                                 int count, float eps, T* __restrict__ y)
+{
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const float* ot = o + (size_t)t * count;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) ss += ot[i] * ot[i];
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)count + eps);
+    for (int i = threadIdx.x; i < count; i += blockDim.x)
+        y[(size_t)t * count + i] = from_f<T>(ot[i] * r * w[i] * sigmoid_f(to_f(gate[(size_t)t * ld_gate + i])));
+}
+
+// ------------------------------------------------------------------------------------------------ routed experts
+// Router: logits = router x (float), softmax over all experts, the `top` largest (ties: the lower index), their scores as weights.
+__global__ void route_kernel(const float* __restrict__ x, const float* __restrict__ router, int width, int experts, int top,
+                             int* __restrict__ ids, float* __restrict__ wts)
+{
+    extern __shared__ float sm[];
+    float* xs = sm;
+    float* z = sm + width;
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = x[(size_t)t * width + i];
+    __syncthreads();
+    for (int e = warp; e < experts; e += nw) {
+        const float* row = router + (size_t)e * width;
+        float part = 0.f;
+        for (int i = lane; i < width; i += 32) part = fmaf(row[i], xs[i], part);
+        part = warp_sum(part);
+        if (lane == 0) z[e] = part;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float mx = z[0];
+        for (int e = 1; e < experts; ++e) mx = fmaxf(mx, z[e]);
+        float sum = 0.f;
+        for (int e = 0; e < experts; ++e) { z[e] = expf(z[e] - mx); sum += z[e]; }
+        const float inv = 1.0f / sum;
+        for (int k = 0; k < top; ++k) {
+            int best = -1;
+            float bv = -1.0f;
+            for (int e = 0; e < experts; ++e)
+                if (z[e] > bv) { bv = z[e]; best = e; }
+            ids[(size_t)t * top + k] = best;
+            wts[(size_t)t * top + k] = bv * inv;
+            z[best] = -2.0f;
+        }
+    }
+}
+
+// One block per (row, chosen expert): mid = silu(gate_e x) * (up_e x), out[t, k] = weight * down_e mid.  Expert weights are
+// stacked: gate, up [experts, ff, width], down [experts, width, ff].  The k partial results are summed by the norm that follows.
+template <typename T>
+__global__ void expert_kernel(const T* __restrict__ x, const T* __restrict__ gate, const T* __restrict__ up, const T* __restrict__ down,
+                              const int* __restrict__ ids, const float* __restrict__ wts, int width, int ff, int top,
+                              float* __restrict__ out)
+{
+    extern __shared__ float sm[];
+    float* xs = sm;
+    float* mid = sm + width;
+    const int t = blockIdx.x, k = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int e = ids[(size_t)t * top + k];
+    const float wt = wts[(size_t)t * top + k];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(x[(size_t)t * width + i]);
+    __syncthreads();
+    const T* ge = gate + (size_t)e * ff * width;
+    const T* ue = up + (size_t)e * ff * width;
+    for (int f = warp; f < ff; f += nw) {
+        float a = 0.f, b = 0.f;
+        for (int i = lane; i < width; i += 32) {
+            a = fmaf(to_f(ge[(size_t)f * width + i]), xs[i], a);
+            b = fmaf(to_f(ue[(size_t)f * width + i]), xs[i], b);
+        }
+        a = warp_sum(a);
+        b = warp_sum(b);
+        if (lane == 0) mid[f] = silu_f(a) * b;
+    }
+    __syncthreads();
+    const T* de = down + (size_t)e * width * ff;
+    float* o = out + ((size_t)t * top + k) * width;
+    for (int c = warp; c < width; c += nw) {
+        float a = 0.f;
+        for (int i = lane; i < ff; i += 32) a = fmaf(to_f(de[(size_t)c * ff + i]), mid[i], a);
+        a = warp_sum(a);
+        if (lane == 0) o[c] = wt * a;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ arg-max of float rows
+__global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int vocab, int* __restrict__ out)
+{
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x)
+        if (row[i] > best) { best = row[i]; at = i; }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ov > best || (ov == best && oi < at)) { best = ov; at = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) { bv[warp] = best; bi[warp] = at; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < nw; ++i)
+            if (bv[i] > best || (bv[i] == best && bi[i] < at)) { best = bv[i]; at = bi[i]; }
+        out[blockIdx.x] = at == 0x7fffffff ? 0 : at;
+    }
+}
+
+}  // namespace b200h
+
+// ===================================================================================================== C ABI
+using namespace b200h;
+
+static thread_local const char* g_error = "";
+
+static int fail(int code, const char* what)
+{
+    g_error = what;
+    return code;
+}
+
+static int launched(const char* what)
+{
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        g_error = cudaGetErrorString(e);
+        (void)what;
+        return (int)e;
+    }
+    return 0;
+}
+
+#define B200H_DISPATCH_T(dtype, ...)                                               \
+    if ((dtype) == B200H_F32) { typedef float T; __VA_ARGS__; }                    \
+    else if ((dtype) == B200H_BF16) { typedef bf16 T; __VA_ARGS__; }               \
+    else return fail(B200H_ERR_UNSUPPORTED, "dtype: float32 (2) or bfloat16 (1)");
+
+static Rotary make_rotary(const b200h_rotary* r)
+{
+    Rotary o;
+    o.freqs = reinterpret_cast<const double*>(r->freqs);
+    o.pairs = r->pairs;
+    o.magnitude = r->magnitude;
+    return o;
+}
+
+B200H_API const char* b200h_last_error(void) { return g_error; }
+
+B200H_API int b200h_embed(const void* tokens, const void* table, float scale, void* out, int n, int width, int dtype, void* stream)
+{
+    if (!tokens || !table || !out || n < 0 || width <= 0) return fail(B200H_ERR_INVALID_ARG, "embed: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, embed_kernel<T><<<n, 256, 0, st>>>((const int*)tokens, (const T*)table, scale, (float*)out, width));
+    return launched("embed");
+}
+
+B200H_API int b200h_causal_conv(const void* x, const void* w, void* state, int64_t slot_stride, const void* tok_seq, const void* cu_q,
+                                const void* seq_slot, void* out, int n, int batch, int width, int taps, int dtype, void* stream)
+{
+    if (!x || !w || !state || !tok_seq || !cu_q || !seq_slot || !out || width <= 0 || batch <= 0)
+        return fail(B200H_ERR_INVALID_ARG, "causal_conv: bad arguments");
+    if (taps < 1 || taps > B200H_MAX_TAPS) return fail(B200H_ERR_UNSUPPORTED, "causal_conv: taps out of range");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, conv_kernel<T><<<n, 256, 0, st>>>((const float*)x, (const float*)w, (const float*)state, slot_stride,
+                                                             (const int*)tok_seq, (const int*)cu_q, (const int*)seq_slot, (T*)out,
+                                                             width, taps));
+    if (taps > 1)
+        conv_state_kernel<<<dim3((width + 127) / 128, batch), 128, 0, st>>>((const float*)x, (float*)state, slot_stride, (const int*)cu_q,
+                                                                           (const int*)seq_slot, width, taps);
+    return launched("causal_conv");
+}
+
+B200H_API int b200h_residual_group_norm(void* x, const void* m, int m_is_f32, int parts, const void* w, int n, int width, int groups,
+                                        float eps, void* x_t, int dtype, void* stream)
+{
+    if (!x || !m || !w || width <= 0 || groups <= 0 || width % groups || parts < 1)
+        return fail(B200H_ERR_INVALID_ARG, "residual_group_norm: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const dim3 grid(n, groups);
+    if (m_is_f32) {
+        B200H_DISPATCH_T(dtype, residual_group_norm_kernel<float, T><<<grid, 256, 0, st>>>((float*)x, (const float*)m, parts, (const float*)w,
+                                                                                          width, groups, eps, (T*)x_t));
+    } else {
+        B200H_DISPATCH_T(dtype, residual_group_norm_kernel<T, T><<<grid, 256, 0, st>>>((float*)x, (const T*)m, parts, (const float*)w, width,
+                                                                                      groups, eps, (T*)x_t));
+    }
+    return launched("residual_group_norm");
+}
+
+B200H_API int b200h_group_norm_rows(const void* x, const void* rows, const void* w, int count, int width, int groups, float eps, void* out,
+                                    int dtype, void* stream)
+{
+    if (!x || !w || !out || width <= 0 || groups <= 0 || width % groups) return fail(B200H_ERR_INVALID_ARG, "group_norm_rows: bad arguments");
+    if (count == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, group_norm_rows_kernel<T><<<dim3(count, groups), 256, 0, st>>>((const float*)x, (const int*)rows, (const float*)w,
+                                                                                          width, groups, eps, (T*)out));
+    return launched("group_norm_rows");
+}
+
+B200H_API int b200h_depth_mix(void* x, void* hist, int64_t hist_stride, const void* coef, int terms, int64_t count, void* stream)
+{
+    if (!x || !hist || !coef || terms < 1) return fail(B200H_ERR_INVALID_ARG, "depth_mix: bad arguments");
+    if (count == 0) return 0;
+    depth_mix_kernel<<<(unsigned)((count + 255) / 256), 256, 0, (cudaStream_t)stream>>>((float*)x, (float*)hist, hist_stride,
+                                                                                       (const float*)coef, terms, count);
+    return launched("depth_mix");
+}
+
+B200H_API int b200h_latent_prep(const b200h_latent_args* a)
+{
+    if (!a || !a->dq || !a->dkv || !a->q_norm || !a->kv_norm || !a->cq || !a->block_ptrs || !a->tok_seq || !a->tok_pos || !a->cu_blocks)
+        return fail(B200H_ERR_INVALID_ARG, "latent_prep: bad arguments");
+    if (2 * a->rot.pairs > a->rot_dim) return fail(B200H_ERR_INVALID_ARG, "latent_prep: more rotated pairs than rot_dim holds");
+    if (a->n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)a->stream;
+    B200H_DISPATCH_T(a->dtype, latent_prep_kernel<T><<<a->n, 128, 0, st>>>(
+        (const T*)a->dq, a->ld_dq, a->q_rank, (const float*)a->q_norm, (const T*)a->dkv, a->ld_dkv, a->kv_rank, a->rot_dim,
+        (const float*)a->kv_norm, a->eps, make_rotary(&a->rot), (const int*)a->tok_seq, (const int*)a->tok_pos,
+        (const int64_t*)a->block_ptrs, (const int*)a->cu_blocks, a->layer_off, a->block_len, a->rot_off, (T*)a->cq));
+    return launched("latent_prep");
+}
+
+template <typename T>
+static int launch_latent_attention(const b200h_latent_args* a, cudaStream_t st)
+{
+    const int hpb = a->heads < 4 ? a->heads : 4;
+    const dim3 grid(a->n, (a->heads + hpb - 1) / hpb), block(32, hpb);
+    const int nc = (a->kv_rank + 31) / 32, nr = (a->rot_dim + 31) / 32;
+#define B200H_ATT(NC, NR)                                                                                                          \
+    latent_attention_kernel<T, NC, NR><<<grid, block, 0, st>>>((const float*)a->q_lat, (const float*)a->q_rot, (const float*)a->sink, \
+        a->heads, a->kv_rank, a->rot_dim, (const int*)a->tok_seq, (const int*)a->tok_pos, (const int64_t*)a->block_ptrs,            \
+        (const int*)a->cu_blocks, a->layer_off, a->block_len, a->rot_off, (float*)a->o_lat)
+#define B200H_ATT_R(NC)                                    \
+    if (nr <= 1) B200H_ATT(NC, 1);                         \
+    else if (nr <= 2) B200H_ATT(NC, 2);                    \
+    else B200H_ATT(NC, 4)
+    if (nc <= 1) { B200H_ATT_R(1); }
+    else if (nc <= 2) { B200H_ATT_R(2); }
+    else if (nc <= 4) { B200H_ATT_R(4); }
+    else if (nc <= 8) { B200H_ATT_R(8); }
+    else { B200H_ATT_R(16); }
+#undef B200H_ATT_R
+#undef B200H_ATT
+    return 0;
+}
+
+B200H_API int b200h_latent_attention(const b200h_latent_args* a)
+{
+    if (!a || !a->q || !a->uk || !a->uv || !a->gate || !a->sink || !a->q_lat || !a->q_rot || !a->o_lat || !a->y || !a->block_ptrs ||
+        !a->tok_seq || !a->tok_pos || !a->cu_blocks)
+        return fail(B200H_ERR_INVALID_ARG, "latent_attention: bad arguments");
+    if (a->kv_rank > 512 || a->rot_dim > 128) return fail(B200H_ERR_UNSUPPORTED, "latent_attention: kv_rank <= 512 and rot_dim <= 128");
+    if (a->n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)a->stream;
+    const dim3 rows_heads(a->n, a->heads);
+    B200H_DISPATCH_T(a->dtype, latent_query_kernel<T><<<rows_heads, 128, a->dim * sizeof(float), st>>>(
+        (const T*)a->q, a->ld_q, (const T*)a->uk, a->heads, a->dim, a->rot_dim, a->kv_rank, a->scale, make_rotary(&a->rot),
+        (const int*)a->tok_pos, (float*)a->q_lat, (float*)a->q_rot));
+    B200H_DISPATCH_T(a->dtype, launch_latent_attention<T>(a, st));
+    B200H_DISPATCH_T(a->dtype, latent_out_kernel<T><<<rows_heads, 128, a->kv_rank * sizeof(float), st>>>(
+        (const float*)a->o_lat, (const T*)a->uv, (const T*)a->gate, a->ld_gate, a->heads, a->vdim, a->kv_rank, (T*)a->y));
+    return launched("latent_attention");
+}
+
+B200H_API int b200h_decay_attention(const void* q, const void* k, const void* v, int64_t ld, const void* decay, void* state,
+                                    int64_t slot_stride, const void* cu_q, const void* seq_slot, int batch, int heads, int dim, int vdim,
+                                    void* out, int dtype, void* stream)
+{
+    if (!q || !k || !v || !decay || !state || !cu_q || !seq_slot || !out || batch <= 0 || heads <= 0)
+        return fail(B200H_ERR_INVALID_ARG, "decay_attention: bad arguments");
+    if (dim > 256) return fail(B200H_ERR_UNSUPPORTED, "decay_attention: dim <= 256");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int cols = vdim < 8 ? vdim : 8;
+    const dim3 grid((vdim + cols - 1) / cols, heads, batch), block(32, cols);
+    const int nw = (dim + 31) / 32;
+#define B200H_SCAN(NW)                                                                                                                   \
+    decay_scan_kernel<T, NW><<<grid, block, 0, st>>>((const T*)q, (const T*)k, (const T*)v, ld, (const float*)decay, (float*)state,       \
+                                                     slot_stride, (const int*)cu_q, (const int*)seq_slot, heads, dim, vdim, (float*)out)
+    B200H_DISPATCH_T(dtype, if (nw <= 1) B200H_SCAN(1); else if (nw <= 2) B200H_SCAN(2); else if (nw <= 4) B200H_SCAN(4); else B200H_SCAN(8));
+#undef B200H_SCAN
+    return launched("decay_attention");
+}
+
+B200H_API int b200h_gated_rms(const void* o, const void* w, const void* gate, int64_t ld_gate, int n, int count, float eps, void* y,
+                              int dtype, void* stream)
+{
+    if (!o || !w || !gate || !y || count <= 0) return fail(B200H_ERR_INVALID_ARG, "gated_rms: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, gated_rms_kernel<T><<<n, 256, 0, st>>>((const float*)o, (const float*)w, (const T*)gate, ld_gate, count, eps, (T*)y));
+    return launched("gated_rms");
+}
+
+B200H_API int b200h_route(const void* x, const void* router, int n, int width, int experts, int top, void* ids, void* wts, void* stream)
+{
+    if (!x || !router || !ids || !wts || experts <= 0 || top <= 0 || top > experts) return fail(B200H_ERR_INVALID_ARG, "route: bad arguments");
+    if (n == 0) return 0;
+    const size_t smem = (size_t)(width + experts) * sizeof(float);
+    if (smem > 200 * 1024) return fail(B200H_ERR_UNSUPPORTED, "route: width + experts exceeds shared memory");
+    if (smem > 48 * 1024) cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    route_kernel<<<n, 256, smem, (cudaStream_t)stream>>>((const float*)x, (const float*)router, width, experts, top, (int*)ids, (float*)wts);
+    return launched("route");
+}
+
+B200H_API int b200h_experts(const void* x, const void* gate, const void* up, const void* down, const void* ids, const void* wts, int n,
+                            int width, int ff, int top, void* out, int dtype, void* stream)
+{
+    if (!x || !gate || !up || !down || !ids || !wts || !out || ff <= 0) return fail(B200H_ERR_INVALID_ARG, "experts: bad arguments");
+    if (n == 0) return 0;
+    const size_t smem = (size_t)(width + ff) * sizeof(float);
+    if (smem > 200 * 1024) return fail(B200H_ERR_UNSUPPORTED, "experts: width + ff exceeds shared memory");
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(expert_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        expert_kernel<T><<<dim3(n, top), 256, smem, st>>>((const T*)x, (const T*)gate, (const T*)up, (const T*)down, (const int*)ids,
+                                                         (const float*)wts, width, ff, top, (float*)out);
+    });
+    return launched("experts");
+}
+
+B200H_API int b200h_argmax(const void* logits, int64_t ld, int rows, int vocab, void* out, void* stream)
+{
+    if (!logits || !out || vocab <= 0) return fail(B200H_ERR_INVALID_ARG, "argmax: bad arguments");
+    if (rows == 0) return 0;
+    argmax_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((const float*)logits, ld, vocab, (int*)out);
+    return launched("argmax");
+}
+

@@ -68,6 +68,13 @@ class TurboMind:
         self.spec = spec
         self.eos_id = eos_id
         self.max_batch = cfg.max_batch_size or DEFAULT_MAX_BATCH_SIZE
+        self.hybrid = bool(getattr(spec, "hybrid", False))
+        self._lock = threading.Lock()
+        self._next_session = 0
+        self.h2d_bytes = self.d2h_bytes = 0          # running totals of the step traffic (bench.py reports them per step)
+        if self.hybrid:
+            self._init_hybrid(cfg, model, num_blocks, seed)
+            return
         # session_len left unset: what _get_and_verify_max_len derives from the HF config (converter.py get_tm_config step 4;
         # loader.default_session_len), 2048 when the config names no context length
         self.session_len = cfg.session_len or spec.session_len or spec.max_position_embeddings or 2048
@@ -114,11 +121,41 @@ class TurboMind:
         self.h_block_ptrs = torch.zeros(B * self._max_blocks, dtype=torch.int64).pin_memory()
         self._h_block_ptrs = self.h_block_ptrs.numpy()
         self._last_block_ids = None
-        self.h2d_bytes = self.d2h_bytes = 0          # running totals of the step traffic (bench.py reports them per step)
-        self._lock = threading.Lock()
-        self._next_session = 0
         self._use_graphs = os.environ.get("B200_ENGINE_GRAPHS", "1") != "0"
         self._graphs, self._seen_sizes = {}, set()
+
+    def _init_hybrid(self, cfg, model, num_blocks, seed):
+        """Engine state for a hybrid decoder (specs.HybridSpec): the same scheduler and block pool, plus recurrent-state slots,
+        one per batch slot.  A step may carry whole prompt portions (up to max_prefill_token_num rows), so the per-step
+        arrays are packed on the host into one pinned buffer sized by the step and uploaded with one copy."""
+        from .hybrid import HybridModel
+        spec = self.spec
+        if cfg.tp != 1 or self.channel is not None:
+            raise NotImplementedError("hybrid decoders run on one GPU")
+        if cfg.quant_policy != 0:
+            raise NotImplementedError("hybrid decoders keep their latent cache in the projection type (quant_policy 0)")
+        if cfg.enable_prefix_caching:
+            raise NotImplementedError("prefix caching with recurrent state (the state at a block border is not kept)")
+        self.session_len = cfg.session_len or spec.session_len or 2048
+        self.block_len = cfg.cache_block_seq_len
+        self.model = model or HybridModel(spec, block_len=self.block_len, max_batch=self.max_batch)
+        if model is None:
+            self.model.load_synthetic(seed)
+        dev = self.model.device
+        if num_blocks is None:
+            if cfg.cache_max_entry_count >= 1:
+                num_blocks = int(cfg.cache_max_entry_count)
+            else:
+                free, _ = torch.cuda.mem_get_info(dev)
+                num_blocks = int(free * cfg.cache_max_entry_count) // self.model.block_bytes
+        self.pool = self.model.make_cache(num_blocks)
+        self.state = self.model.make_state(self.max_batch)
+        budget = max(self.max_batch, cfg.max_prefill_token_num)
+        self.scheduler = Scheduler(max_batch=self.max_batch, block_len=self.block_len, num_blocks=num_blocks,
+                                   session_len=self.session_len, prefix_caching=False,
+                                   prefill_chunk=max(1, cfg.max_prefill_token_num), token_budget=budget, state_slots=self.max_batch)
+        self.last_logits = None          # float logits [rows, vocab] of the last step and the row each belongs to
+        self.last_rows = {}
 
     @classmethod
     def from_pretrained(cls, pretrained_model_name_or_path, engine_config=None, **kw):
@@ -134,7 +171,7 @@ class TurboMind:
             spec, model, eos = load_hf_checkpoint(pretrained_model_name_or_path, quant_policy=cfg.quant_policy,
                                                   block_len=cfg.cache_block_seq_len, hf_overrides=cfg.hf_overrides,
                                                   model_format=cfg.model_format,
-                                                  max_batch=cfg.max_batch_size or DEFAULT_MAX_BATCH_SIZE)
+                                                  max_batch=cfg.max_batch_size or DEFAULT_MAX_BATCH_SIZE, dtype=cfg.dtype)
             return cls(spec, cfg, model=model, eos_id=eos, **kw)
         raise FileNotFoundError(pretrained_model_name_or_path)
 
@@ -142,11 +179,12 @@ class TurboMind:
         return TurboMindInstance(self)
 
     # ------------------------------------------------------------------ one engine step
-    def step(self):
+    def step(self, plan=None):
         """Schedule + run one step for the active batch; returns [(sequence, token|None)] events.  Under tensor
-        parallelism only the leader (rank 0) calls this; it publishes the step's arrays to the followers first."""
+        parallelism only the leader (rank 0) calls this; it publishes the step's arrays to the followers first.
+        plan: {session id: tokens to feed} runs exactly that batch instead of the scheduler's choice (Scheduler.schedule_planned)."""
         sched = self.scheduler
-        batch = sched.schedule()
+        batch = sched.schedule() if plan is None else sched.schedule_planned(plan)
         if not batch:
             # a tick may legitimately form no batch (it only retired or preempted); a long run of them with work pending
             # means the scheduler cannot make progress -- fail loudly instead of spinning in the callers' loops
@@ -158,16 +196,76 @@ class TurboMind:
         st = marshal_step(batch)
         if self.channel is not None:
             self.channel.publish(st)
-        out = self._execute(st)
         cu_q = st["cu_q_len"]
         rows = [cu_q[i + 1] - 1 for i in range(len(batch))]                              # sample = last row of each sequence
+        # rows whose logits a caller asked for by position (Sequence.logit_positions)
+        asked = [(s, p, cu_q[i] + p - s.cached) for i, s in enumerate(batch) for p in s.logit_positions
+                 if s.cached <= p < s.cached + s.step_tokens]
+        if self.hybrid:
+            out = self._execute_hybrid(st, batch, rows + [r for _, _, r in asked])
+        else:
+            out = self._execute(st)
         sampled = [out[r] for r in rows]
         if any(s.sampling is not None for s in batch):
             self._sample(batch, rows, sampled)
+        if asked:
+            lg = self._logits_of_rows([r for _, _, r in asked], st["token_num"])
+            for (s, p, _), row in zip(asked, lg):
+                s.position_logits[p] = row
+                s.logit_positions.remove(p)
         events = sched.update(batch, sampled)
         if any(s.want_logits or s.want_logprobs for s in batch):
             self._collect_extras(batch, rows, events, st["token_num"])
         return events
+
+    def _logits_of_rows(self, rows, token_num):
+        """Float logits [len(rows), vocab] on the host for rows of the step that just ran."""
+        if self.hybrid:
+            idx = torch.tensor([self.last_rows[r] for r in rows], dtype=torch.long, device=self.last_logits.device)
+            return self.last_logits.index_select(0, idx).cpu()
+        lg = self.model.logits(token_num)[:, :self.spec.vocab]
+        return lg[torch.tensor(rows, dtype=torch.long, device=lg.device)].float().cpu()
+
+    def _execute_hybrid(self, st, batch, rows):
+        """One step of a hybrid decoder: zero the state slot of every sequence that starts (position 0), pack the step's arrays
+        [tokens n | tok_seq n | tok_pos n | cu_q B+1 | cu_blocks B+1 | seq_slot B | rows r] into one pinned buffer, upload,
+        run HybridModel.step, arg-max the last row of every sequence.  Returns {row: greedy id}."""
+        import numpy as np
+        B, n = st["batch_size"], st["token_num"]
+        dev = self.model.device
+        for s in batch:
+            if s.cached == 0:
+                self.state.reset(s.slot)
+        cu_q, cu_k = st["cu_q_len"], st["cu_k_len"]
+        uniq = list(dict.fromkeys(rows))
+        r = len(uniq)
+        ctl = np.empty(3 * n + 2 * (B + 1) + B + r, np.int32)
+        ctl[:n] = st["token_ids"]
+        for i in range(B):
+            lo, hi = cu_q[i], cu_q[i + 1]
+            end = cu_k[i + 1] - cu_k[i]
+            ctl[n + lo:n + hi] = i
+            ctl[2 * n + lo:2 * n + hi] = np.arange(end - (hi - lo), end, dtype=np.int32)
+        o = 3 * n
+        ctl[o:o + B + 1] = cu_q
+        ctl[o + B + 1:o + 2 * B + 2] = st["cu_block_nums"]
+        ctl[o + 2 * B + 2:o + 3 * B + 2] = [s.slot for s in batch]
+        ctl[o + 3 * B + 2:] = uniq
+        ptrs = np.asarray(st["block_ids"], np.int64) * self.pool.block_bytes + self.pool.base
+        pin = dev.type == "cuda"
+        h_ctl = torch.from_numpy(ctl)
+        h_ptrs = torch.from_numpy(ptrs)
+        d_ctl = (h_ctl.pin_memory() if pin else h_ctl).to(dev, non_blocking=True)
+        d_ptrs = (h_ptrs.pin_memory() if pin else h_ptrs).to(dev, non_blocking=True)
+        self.h2d_bytes += ctl.nbytes + ptrs.nbytes
+        logits = self.model.step(n=n, batch=B, tokens=d_ctl[:n], tok_seq=d_ctl[n:2 * n], tok_pos=d_ctl[2 * n:3 * n],
+                                 cu_q=d_ctl[o:o + B + 1], cu_blocks=d_ctl[o + B + 1:o + 2 * B + 2],
+                                 seq_slot=d_ctl[o + 2 * B + 2:o + 3 * B + 2], block_ptrs=d_ptrs, state=self.state,
+                                 rows=d_ctl[o + 3 * B + 2:], n_rows=r, trace=getattr(self, "layer_trace", None))
+        self.last_logits, self.last_rows = logits, {row: k for k, row in enumerate(uniq)}
+        ids = self.model.argmax(logits).cpu().tolist()
+        self.d2h_bytes += 4 * r
+        return {row: ids[k] for k, row in enumerate(uniq)}
 
     def _sample(self, batch, rows, sampled):
         """do_sample sequences that produce a token in this step: the device sampling stage (b200_sample: repetition penalty,
@@ -177,7 +275,7 @@ class TurboMind:
         import ctypes as C
         import numpy as np
         from .. import _lib as L
-        lib, dev = self.model.lib, self.model.device
+        lib, dev = L.load(), self.model.device
         items = [(i, s) for i, s in enumerate(batch) if s.sampling is not None and s.cached + s.step_tokens >= s.context_len]
         if not items:
             return
@@ -214,8 +312,14 @@ class TurboMind:
         d_slot = torch.tensor([s.rng_slot for _, s in items], dtype=torch.int32, device=dev)
         d_out = torch.zeros(n, dtype=torch.int32, device=dev)
         p = L.SamplingParams()
-        p.logits, p.ld = lib.b200_model_buffer(self.model.handle, 0), self.model.vocab_local
-        p.dtype, p.count, p.vocab = self.model.cfg.dtype, n, self.spec.vocab
+        if self.hybrid:
+            # the sampling stage reads T logits: the step's float logits as bf16, rows renumbered to that compact tensor
+            lg16 = self.last_logits.to(torch.bfloat16).contiguous()
+            d_rows = torch.tensor([self.last_rows[rows[i]] for i, _ in items], dtype=torch.int32, device=dev)
+            p.logits, p.ld, p.dtype = lg16.data_ptr(), lg16.stride(0), 1
+        else:
+            p.logits, p.ld, p.dtype = lib.b200_model_buffer(self.model.handle, 0), self.model.vocab_local, self.model.cfg.dtype
+        p.count, p.vocab = n, self.spec.vocab
         p.rows, p.temperature, p.top_k, p.top_p, p.min_p = (d_rows.data_ptr(), d_t.data_ptr(), d_k.data_ptr(), d_p.data_ptr(),
                                                             d_m.data_ptr())
         hist = None
@@ -243,9 +347,12 @@ class TurboMind:
         for s, tok in events:
             if tok is None or not (s.want_logits or s.want_logprobs):
                 continue
-            if lg is None:
-                lg = self.model.logits(token_num)[:, :self.spec.vocab].float()
-            row = lg[row_of[id(s)]]
+            if self.hybrid:
+                row = self.last_logits[self.last_rows[row_of[id(s)]]]
+            else:
+                if lg is None:
+                    lg = self.model.logits(token_num)[:, :self.spec.vocab].float()
+                row = lg[row_of[id(s)]]
             if s.want_logits:
                 s.logits.append(row.cpu())
             if s.want_logprobs:
@@ -361,6 +468,13 @@ class TurboMindInstance:
         if (seq.want_logits or seq.want_logprobs) and getattr(self.engine, "channel", None) is not None:
             raise NotImplementedError("logits / logprobs outputs under tensor parallelism (the logits are vocabulary-sharded)")
         self.engine.scheduler.add(seq)
+        return seq
+
+    def open(self, session_id, input_ids, gen_config: GenerationConfig = None):
+        """An open-ended request: its input continues (append to the returned Sequence's `prompt` between steps), nothing is
+        sampled for it, and it lives until Scheduler.finish(session_id).  Runs through TurboMind.step(plan) like any other."""
+        seq = self._submit(session_id, input_ids, gen_config)
+        seq.hold = True
         return seq
 
     def stream_infer(self, session_id, input_ids, gen_config: GenerationConfig = None, **kw):

@@ -1,0 +1,304 @@
+"""Device runtime of hybrid decoders (specs.HybridSpec): weights, cache / state geometry and the step function.
+
+A hybrid decoder mixes layer kinds, so a sequence owns two things between steps:
+  * pages of the engine's block pool (runtime.KvCachePool, handed out by scheduler.BlockAllocator) -- every latent-attention
+    layer keeps, per position, its normed key/value latent (as T) and the rotated key part all heads share (as float);
+  * one slot of the StatePool (handed out by scheduler.Scheduler's slot list) -- per layer the last taps-1 inputs of the
+    short convolution, and per decayed-linear-attention layer the [heads, vdim, dim] float state.
+The step is a mixed step like b200_model_chunk_step: any number of rows per sequence, prompt portions beside single decoded
+tokens; kernels address rows through (sequence, position) arrays, pages through the block table, state through the slot.
+
+Compute: every operator except the plain matrix products is a kernel of libb200hybrid.so (csrc/hybrid/hybrid_ops.cu); the
+plain projections are cuBLAS GEMMs through torch (bf16 with float accumulation, or true float32 with TF32 off).  What the
+design wants in 32 bits (residual stream and its history, norms, rotary angles, scores, softmax, recurrent state, router)
+is float in every kernel whatever the projection type is."""
+import ctypes as C
+
+import torch
+
+from .. import _hybrid_lib as H
+from .runtime import KvCachePool
+from .specs import HybridSpec
+
+_TORCH_T = {"bf16": torch.bfloat16, "f32": torch.float32}
+_DT = {"bf16": H.BF16, "f32": H.F32}
+
+
+def _align(n, a=16):
+    return (n + a - 1) // a * a
+
+
+class StatePool:
+    """Recurrent-state slots: one float row per live sequence.  A slot is zeroed when a sequence starts (or restarts after a
+    preemption) in it; the scheduler owns the free list."""
+
+    def __init__(self, slots, floats_per_slot, device):
+        self.slots, self.floats_per_slot = slots, floats_per_slot
+        self.storage = torch.zeros(slots, max(floats_per_slot, 1), dtype=torch.float32, device=device)
+
+    def reset(self, slot):
+        self.storage[slot].zero_()
+
+    def ptr(self, float_offset):
+        return self.storage.data_ptr() + 4 * float_offset
+
+
+class HybridModel:
+    """Weights of one hybrid decoder on one GPU and its step function."""
+    kind = "hybrid"
+    tp_size = 1
+
+    def __init__(self, spec: HybridSpec, *, block_len=64, max_batch=64, device=None):
+        if spec.dtype not in _DT:
+            raise ValueError(f"dtype {spec.dtype!r}: hybrid decoders run in 'bf16' or 'f32'")
+        if not 1 <= spec.conv_taps <= H.MAX_TAPS:
+            raise NotImplementedError(f"conv taps {spec.conv_taps} (1..{H.MAX_TAPS})")
+        if spec.width % spec.norm_groups:
+            raise ValueError(f"width {spec.width} is not divisible into {spec.norm_groups} norm groups")
+        self.lib = H.load()
+        self.spec = spec
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+        self.T, self.dt = _TORCH_T[spec.dtype], _DT[spec.dtype]
+        self.block_len, self.max_batch = block_len, max_batch
+        esize = 2 if spec.dtype == "bf16" else 4
+        # cache page: the latent layers' regions one after another; in a region [block_len, kv_rank] T then [block_len, rot_dim] float
+        # state slot: per layer [taps-1, width] conv inputs, then per decay layer [heads, vdim, dim]
+        self.cache_off, self.rot_off, self.conv_off, self.mix_off = {}, {}, {}, {}
+        page = slot = 0
+        taps = spec.conv_taps
+        for i, layer in enumerate(spec.layers):
+            m = layer.mixer
+            self.conv_off[i] = slot
+            slot += (taps - 1) * spec.width
+            if m.kind == "latent_attention":
+                if m.kv_rank > 512 or m.rot_dim > 128:
+                    raise NotImplementedError("latent attention: kv_rank <= 512 and rot_dim <= 128")
+                self.cache_off[i] = page
+                self.rot_off[i] = _align(block_len * m.kv_rank * esize)
+                page += self.rot_off[i] + _align(block_len * m.rot_dim * 4)
+            elif m.kind == "lightning":
+                if m.dim > 256:
+                    raise NotImplementedError("decayed linear attention: dim <= 256")
+                self.mix_off[i] = slot
+                slot += m.heads * m.vdim * m.dim
+            else:
+                raise NotImplementedError(m.kind)
+        self.block_bytes = max(page, 16)
+        self.layer_bytes = self.block_bytes         # bytes of one block per "layer unit" as the engine sizes pools: whole block
+        self.slot_floats = slot
+        self.w = {}
+        self.weight_bytes = 0
+        if spec.dtype == "f32":
+            # float32 serving means true 32-bit products: no TF32, no reduced-precision accumulation
+            torch.backends.cuda.matmul.allow_tf32 = False
+            torch.backends.cudnn.allow_tf32 = False
+            torch.set_float32_matmul_precision("highest")
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
+    # ------------------------------------------------------------------ pools
+    def make_cache(self, num_blocks):
+        return KvCachePool(num_blocks, 1, 1, block_len=self.block_len, device=self.device, block_bytes=self.block_bytes)
+
+    def make_state(self, slots):
+        return StatePool(slots, self.slot_floats, self.device)
+
+    # ------------------------------------------------------------------ weights
+    def load_weights(self, get):
+        """get(name) -> host tensor by checkpoint name ('embed', 'l<i>.mix.dq', 'l<i>.mlp.e<k>.gate', ...).  Linear weights stay
+        [out, in] as T; projections that read the same input are stacked into one matrix; experts are stacked per layer;
+        everything the kernels read as float (norm, conv, router weights, sinks, decays, depth coefficients) is float."""
+        s, dev, T = self.spec, self.device, self.T
+        w = self.w
+
+        def lin(*names, shape=None):
+            t = torch.cat([get(n).to(torch.float32) for n in names], 0)
+            if shape is not None and tuple(t.shape) != tuple(shape):
+                raise ValueError(f"{'+'.join(names)}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+            t = t.to(dev, T).contiguous()
+            self.weight_bytes += t.numel() * t.element_size()
+            return t
+
+        def f32(name, shape):
+            t = get(name).to(torch.float32)
+            if tuple(t.shape) != tuple(shape):
+                raise ValueError(f"{name}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+            return t.to(dev).contiguous()
+
+        W = s.width
+        w["embed"] = lin("embed", shape=(s.vocab, W))
+        w["head"] = lin("head", shape=(s.vocab, W))
+        w["final.norm"] = f32("final.norm", (W,))
+        for i, layer in enumerate(s.layers):
+            p, m = f"l{i}.", layer.mixer
+            w[p + "norm1"] = f32(p + "norm1", (W,))
+            w[p + "canon1"] = f32(p + "canon1", (W, s.conv_taps))
+            w[p + "dwa"] = f32(p + "dwa", (i + 2,))
+            if m.kind == "latent_attention":
+                HV = m.heads * m.vdim
+                w[p + "in"] = lin(p + "mix.dq", p + "mix.dkv", p + "mix.g", shape=(m.q_rank + m.kv_rank + m.rot_dim + HV, W))
+                w[p + "uq"] = lin(p + "mix.uq", shape=(m.heads * (m.dim + m.rot_dim), m.q_rank))
+                w[p + "uk"] = lin(p + "mix.uk", shape=(m.heads * m.dim, m.kv_rank))
+                w[p + "uv"] = lin(p + "mix.uv", shape=(HV, m.kv_rank))
+                w[p + "o"] = lin(p + "mix.o", shape=(W, HV))
+                w[p + "dq.norm"] = f32(p + "mix.dq.norm", (m.q_rank,))
+                w[p + "dkv.norm"] = f32(p + "mix.dkv.norm", (m.kv_rank,))
+                w[p + "sink"] = f32(p + "mix.sink", (m.heads,))
+                freqs, mag = m.rot.frequencies()
+                w[p + "freqs"] = torch.tensor(freqs, dtype=torch.float64, device=dev)
+                w[p + "mag"] = float(mag)
+            else:
+                HD, HV = m.heads * m.dim, m.heads * m.vdim
+                w[p + "in"] = lin(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g", shape=(2 * HD + 2 * HV, W))
+                w[p + "o"] = lin(p + "mix.o", shape=(W, HV))
+                w[p + "mixnorm"] = f32(p + "mix.norm", (HV,))
+                w[p + "decay"] = torch.tensor(m.decay, dtype=torch.float32, device=dev)
+            f = layer.mlp
+            if f is not None:
+                w[p + "norm2"] = f32(p + "norm2", (W,))
+                w[p + "router"] = f32(p + "mlp.router", (f.experts, W))
+                for part, shape in (("gate", (f.ff, W)), ("up", (f.ff, W)), ("down", (W, f.ff))):
+                    w[p + part] = torch.stack([lin(f"{p}mlp.e{e}.{part}", shape=shape) for e in range(f.experts)]).contiguous()
+        if dev.type == "cuda":
+            torch.cuda.synchronize(dev)
+
+    def load_synthetic(self, seed=0):
+        """Random weights of the spec's shapes (benchmarks and tests)."""
+        g = torch.Generator().manual_seed(seed)
+        taps = self.spec.conv_taps
+
+        def get(name):
+            shape = self.tensor_shapes()[name]
+            if name.endswith(("norm1", "norm2", ".norm")):
+                return 1.0 + 0.1 * torch.randn(shape, generator=g)
+            if name.endswith("canon1"):
+                return torch.randn(shape, generator=g) / taps
+            if name.endswith("dwa"):
+                return torch.softmax(torch.randn(shape, generator=g), 0)
+            if name.endswith("sink"):
+                return torch.randn(shape, generator=g)
+            scale = 0.02 if name == "embed" else 1.0 / (shape[-1] ** 0.5)
+            return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16)
+
+        self.load_weights(get)
+
+    def tensor_shapes(self):
+        """Checkpoint tensor names -> shapes for this spec."""
+        s, W = self.spec, self.spec.width
+        out = {"embed": (s.vocab, W), "head": (s.vocab, W), "final.norm": (W,)}
+        for i, layer in enumerate(s.layers):
+            p, m = f"l{i}.", layer.mixer
+            out.update({p + "norm1": (W,), p + "canon1": (W, s.conv_taps), p + "dwa": (i + 2,)})
+            if m.kind == "latent_attention":
+                HV = m.heads * m.vdim
+                out.update({p + "mix.dq": (m.q_rank, W), p + "mix.dq.norm": (m.q_rank,), p + "mix.uq": (m.heads * (m.dim + m.rot_dim), m.q_rank),
+                            p + "mix.dkv": (m.kv_rank + m.rot_dim, W), p + "mix.dkv.norm": (m.kv_rank,),
+                            p + "mix.uk": (m.heads * m.dim, m.kv_rank), p + "mix.uv": (HV, m.kv_rank), p + "mix.sink": (m.heads,),
+                            p + "mix.g": (HV, W), p + "mix.o": (W, HV)})
+            else:
+                HD, HV = m.heads * m.dim, m.heads * m.vdim
+                out.update({p + "mix.q": (HD, W), p + "mix.k": (HD, W), p + "mix.v": (HV, W), p + "mix.g": (HV, W),
+                            p + "mix.o": (W, HV), p + "mix.norm": (HV,)})
+            f = layer.mlp
+            if f is not None:
+                out.update({p + "norm2": (W,), p + "mlp.router": (f.experts, W)})
+                for e in range(f.experts):
+                    out.update({f"{p}mlp.e{e}.gate": (f.ff, W), f"{p}mlp.e{e}.up": (f.ff, W), f"{p}mlp.e{e}.down": (W, f.ff)})
+        return out
+
+    # ------------------------------------------------------------------ step
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream if self.device.type == "cuda" else None
+
+    def _linear(self, x, w):
+        return torch.mm(x, w.t())
+
+    def step(self, *, n, batch, tokens, tok_seq, tok_pos, cu_q, seq_slot, block_ptrs, cu_blocks, state: StatePool, rows, n_rows,
+             trace=None):
+        """One mixed step.  Device tensors: tokens / tok_seq / tok_pos int32 [n]; cu_q, cu_blocks int32 [batch + 1]; seq_slot
+        int32 [batch]; block_ptrs int64 (page addresses); rows int32 [n_rows] = the rows whose logits are wanted.
+        Returns float logits [n_rows, vocab].  trace: a list that receives a copy of the stream after every layer."""
+        s, lib, w, dev, T, dt = self.spec, self.lib, self.w, self.device, self.T, self.dt
+        W, eps, groups, taps = s.width, s.norm_eps, s.norm_groups, s.conv_taps
+        st = self._stream()
+        L = len(s.layers)
+        f32 = dict(dtype=torch.float32, device=dev)
+        hist = torch.empty(L + 1, n, W, **f32)
+        x = torch.empty(n, W, **f32)
+        H.check(lib.b200h_embed(tokens.data_ptr(), w["embed"].data_ptr(), s.embedding_scale, hist.data_ptr(), n, W, dt, st), "embed")
+        x.copy_(hist[0])
+        h = torch.empty(n, W, dtype=T, device=dev)
+        xt = torch.empty(n, W, dtype=T, device=dev)
+        for i, layer in enumerate(s.layers):
+            p, m = f"l{i}.", layer.mixer
+            H.check(lib.b200h_causal_conv(x.data_ptr(), w[p + "canon1"].data_ptr(), state.ptr(self.conv_off[i]), state.storage.stride(0),
+                                          tok_seq.data_ptr(), cu_q.data_ptr(), seq_slot.data_ptr(), h.data_ptr(), n, batch, W, taps,
+                                          dt, st), "causal_conv")
+            proj = self._linear(h, w[p + "in"])
+            ld, es = proj.stride(0), proj.element_size()
+            if m.kind == "latent_attention":
+                HV = m.heads * m.vdim
+                a = H.LatentArgs()
+                a.n, a.heads, a.dim, a.rot_dim, a.vdim, a.kv_rank, a.q_rank = n, m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
+                a.block_len, a.scale, a.eps = self.block_len, m.scale, eps
+                a.rot = H.Rotary(w[p + "freqs"].data_ptr(), m.rot.dims // 2, w[p + "mag"])
+                a.dq, a.ld_dq = proj.data_ptr(), ld
+                a.dkv, a.ld_dkv = proj.data_ptr() + es * m.q_rank, ld
+                a.gate, a.ld_gate = proj.data_ptr() + es * (m.q_rank + m.kv_rank + m.rot_dim), ld
+                a.q_norm, a.kv_norm, a.sink = w[p + "dq.norm"].data_ptr(), w[p + "dkv.norm"].data_ptr(), w[p + "sink"].data_ptr()
+                cq = torch.empty(n, m.q_rank, dtype=T, device=dev)
+                a.cq = cq.data_ptr()
+                a.tok_seq, a.tok_pos = tok_seq.data_ptr(), tok_pos.data_ptr()
+                a.block_ptrs, a.cu_blocks = block_ptrs.data_ptr(), cu_blocks.data_ptr()
+                a.layer_off, a.rot_off, a.dtype, a.stream = self.cache_off[i], self.rot_off[i], dt, st
+                H.check(lib.b200h_latent_prep(C.byref(a)), "latent_prep")
+                q = self._linear(cq, w[p + "uq"])
+                q_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
+                q_rot = torch.empty(n, m.heads, m.rot_dim, **f32)
+                o_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
+                y = torch.empty(n, HV, dtype=T, device=dev)
+                a.q, a.ld_q, a.uk, a.uv = q.data_ptr(), q.stride(0), w[p + "uk"].data_ptr(), w[p + "uv"].data_ptr()
+                a.q_lat, a.q_rot, a.o_lat, a.y = q_lat.data_ptr(), q_rot.data_ptr(), o_lat.data_ptr(), y.data_ptr()
+                H.check(lib.b200h_latent_attention(C.byref(a)), "latent_attention")
+            else:
+                HD, HV = m.heads * m.dim, m.heads * m.vdim
+                o = torch.empty(n, m.heads, m.vdim, **f32)
+                base = proj.data_ptr()
+                H.check(lib.b200h_decay_attention(base, base + es * HD, base + es * 2 * HD, ld, w[p + "decay"].data_ptr(),
+                                                  state.ptr(self.mix_off[i]), state.storage.stride(0), cu_q.data_ptr(),
+                                                  seq_slot.data_ptr(), batch, m.heads, m.dim, m.vdim, o.data_ptr(), dt, st),
+                        "decay_attention")
+                y = torch.empty(n, HV, dtype=T, device=dev)
+                H.check(lib.b200h_gated_rms(o.data_ptr(), w[p + "mixnorm"].data_ptr(), base + es * (2 * HD + HV), ld, n, HV, eps,
+                                            y.data_ptr(), dt, st), "gated_rms")
+            mixed = self._linear(y, w[p + "o"])
+            f = layer.mlp
+            H.check(lib.b200h_residual_group_norm(x.data_ptr(), mixed.data_ptr(), 0, 1, w[p + "norm1"].data_ptr(), n, W, groups, eps,
+                                                  xt.data_ptr() if f is not None else None, dt, st), "residual_group_norm")
+            if f is not None:
+                ids = torch.empty(n, f.top, dtype=torch.int32, device=dev)
+                wts = torch.empty(n, f.top, **f32)
+                H.check(lib.b200h_route(x.data_ptr(), w[p + "router"].data_ptr(), n, W, f.experts, f.top, ids.data_ptr(), wts.data_ptr(), st),
+                        "route")
+                out = torch.empty(n, f.top, W, **f32)
+                H.check(lib.b200h_experts(xt.data_ptr(), w[p + "gate"].data_ptr(), w[p + "up"].data_ptr(), w[p + "down"].data_ptr(),
+                                          ids.data_ptr(), wts.data_ptr(), n, W, f.ff, f.top, out.data_ptr(), dt, st), "experts")
+                H.check(lib.b200h_residual_group_norm(x.data_ptr(), out.data_ptr(), 1, f.top, w[p + "norm2"].data_ptr(), n, W, groups, eps,
+                                                      None, dt, st), "residual_group_norm")
+            H.check(lib.b200h_depth_mix(x.data_ptr(), hist.data_ptr(), n * W, w[p + "dwa"].data_ptr(), i + 2, n * W, st), "depth_mix")
+            if trace is not None:
+                trace.append(x.clone())
+        xn = torch.empty(n_rows, W, dtype=T, device=dev)
+        H.check(lib.b200h_group_norm_rows(x.data_ptr(), rows.data_ptr(), w["final.norm"].data_ptr(), n_rows, W, groups, eps, xn.data_ptr(),
+                                          dt, st), "group_norm_rows")
+        if T is torch.float32:
+            return torch.mm(xn, w["head"].t())
+        return torch.mm(xn, w["head"].t(), out_dtype=torch.float32)
+
+    def argmax(self, logits):
+        """Greedy ids of float logits [r, vocab] (device int32 [r])."""
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        st = self._stream()
+        H.check(self.lib.b200h_argmax(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], out.data_ptr(), st), "argmax")
+        return out

@@ -317,11 +317,40 @@ def deep_merge(base, override):
     return base
 
 
-def load_hf_checkpoint(path, *, quant_policy=0, block_len=64, max_batch=64, tp=1, rank=0, hf_overrides=None, model_format=None):
+def load_hybrid_checkpoint(cfg, tensors, *, name, block_len=64, max_batch=64, dtype="auto"):
+    """A checkpoint whose config.json names one of specs.HYBRID_ARCHITECTURES -> (HybridSpec, HybridModel on the GPU, None).
+    dtype: 'auto' / 'bfloat16' serve in bf16 (the checkpoint's own type), 'float32' in true 32-bit."""
+    import dataclasses
+    from .hybrid import HybridModel
+    from .specs import HYBRID_ARCHITECTURES
+    spec = HYBRID_ARCHITECTURES[cfg["architecture"]](cfg, name=name)
+    if dtype not in ("auto", "bfloat16", "float32"):
+        raise ValueError(f"dtype {dtype!r}: hybrid decoders serve in bfloat16 or float32")
+    spec = dataclasses.replace(spec, dtype="f32" if dtype == "float32" else "bf16")
+    model = HybridModel(spec, block_len=block_len, max_batch=max_batch)
+    expected = model.tensor_shapes()
+    missing = sorted(k for k in expected if k not in tensors)
+    if missing:
+        raise KeyError(f"checkpoint lacks {len(missing)} tensors, e.g. {missing[:4]}")
+    model.load_weights(lambda k: tensors[k])
+    eos = cfg.get("eos_token_id")
+    return spec, model, eos[0] if isinstance(eos, list) else eos
+
+
+def load_hf_checkpoint(path, *, quant_policy=0, block_len=64, max_batch=64, tp=1, rank=0, hf_overrides=None, model_format=None,
+                       dtype="auto"):
     from .runtime import DecodeModel, _TORCH_T
     cfg, tensors = read_checkpoint(path)
     if hf_overrides:
         deep_merge(cfg, hf_overrides)
+    from .specs import HYBRID_ARCHITECTURES
+    if cfg.get("architecture") in HYBRID_ARCHITECTURES:
+        if tp != 1:
+            raise NotImplementedError("hybrid decoders run on one GPU")
+        return load_hybrid_checkpoint(cfg, tensors, name=os.path.basename(os.path.normpath(path)), block_len=block_len,
+                                      max_batch=max_batch, dtype=dtype)
+    if dtype == "float32":
+        raise NotImplementedError("float32 serving exists for hybrid decoders only; this architecture runs in float16 / bfloat16")
     method = (cfg.get("quantization_config") or {}).get("quant_method")
     if method is not None and model_format not in (None, method):
         # get_tm_config: the user's model_format must agree with the checkpoint's own quantization_config (converter.py)

@@ -31,9 +31,11 @@ class KvCachePool:
     """Flat pool of fixed-size KV blocks; one block holds block_len tokens of ALL layers
     (unified_attention_layer.cc:163-171)."""
 
-    def __init__(self, num_blocks, layers, kv_heads, head_dim=128, block_len=64, quant_policy=8, device="cuda"):
+    def __init__(self, num_blocks, layers, kv_heads, head_dim=128, block_len=64, quant_policy=8, device="cuda", block_bytes=None):
+        """block_bytes: the size of one block when its content is not `layers` uniform K/V regions (hybrid decoders lay out
+        a block themselves, turbomind/hybrid.py)."""
         self.layer_bytes = kv_layer_bytes(kv_heads, block_len, head_dim, quant_policy)
-        self.block_bytes = self.layer_bytes * layers
+        self.block_bytes = self.layer_bytes * layers if block_bytes is None else int(block_bytes)
         self.block_len = block_len
         self.num_blocks = num_blocks
         self.storage = torch.zeros(num_blocks * self.block_bytes, dtype=torch.uint8, device=device)

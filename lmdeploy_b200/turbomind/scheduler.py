@@ -54,6 +54,10 @@ class Sequence:
     chain: List[int] = field(default_factory=list)      # prefix-cache identity of each full block so far
     sampling: Optional[dict] = None   # do_sample requests: temperature / top_k / top_p / min_p / repetition_penalty / seed
     rng_slot: int = -1                # ... and the device RNG state slot the engine gave it
+    slot: int = -1                    # recurrent-state slot (models that carry state besides the paged cache)
+    hold: bool = False                # open-ended input: the caller appends to `prompt` between steps and ends the request itself
+    logit_positions: List[int] = field(default_factory=list)   # positions whose logits the caller wants ...
+    position_logits: Dict[int, object] = field(default_factory=dict)   # ... and those logits once their step has run
 
     def token_at(self, pos):
         return self.prompt[pos] if pos < len(self.prompt) else self.generated[pos - len(self.prompt)]
@@ -184,8 +188,13 @@ class PrefixCache:
 
 class Scheduler:
     def __init__(self, *, max_batch, block_len, num_blocks, session_len, prefix_caching=False, prefill_chunk=1,
-                 token_budget=None):
+                 token_budget=None, state_slots=None):
+        """state_slots: number of recurrent-state slots (None: the model keeps no state outside the paged cache).  A running
+        sequence holds exactly one; it is taken at admission and returned with the blocks (retirement, preemption)."""
         self.max_batch, self.block_len, self.session_len = max_batch, block_len, session_len
+        self.slots = None if state_slots is None else list(range(int(state_slots) - 1, -1, -1))
+        if self.slots is not None and prefix_caching:
+            raise ValueError("prefix caching needs the state at a block border, which recurrent-state slots do not keep")
         self.prefill_chunk = max(1, int(prefill_chunk))
         self.token_budget = max(max_batch, token_budget or max_batch)
         self.alloc = BlockAllocator(num_blocks)
@@ -219,6 +228,9 @@ class Scheduler:
         blocks = seq.blocks if self.prefix is None else self.prefix.release(seq.blocks)
         self.alloc.release(blocks)
         seq.blocks = []
+        if seq.slot >= 0:
+            self.slots.append(seq.slot)
+            seq.slot = -1
 
     def _retire(self):
         """Give back the blocks and the session slot of every finished active sequence."""
@@ -243,6 +255,45 @@ class Scheduler:
 
     def _blocks_needed(self, seq, upto_tokens):
         return (upto_tokens + self.block_len - 1) // self.block_len - len(seq.blocks)
+
+    def schedule_planned(self, plan):
+        """Form exactly the batch the caller names: plan = {session id: tokens to feed this step}, in batch order.  Named
+        sequences that still wait are admitted (state slot, blocks); sequences not named sit the step out and keep what
+        they hold.  Used to replay a recorded schedule through the same allocator, slots and step as schedule()."""
+        self.tick += 1
+        self._retire()
+        batch = []
+        for sid, n in plan.items():
+            s = self.sessions.get(sid)
+            if s is None or s.finished:
+                raise KeyError(f"session {sid} is not live")
+            if n < 1 or s.cached + n > s.context_len:
+                raise ValueError(f"session {sid}: {n} tokens planned, {s.context_len - s.cached} available")
+            if s not in self.active:
+                if len(self.active) >= self.max_batch or (self.slots is not None and not self.slots):
+                    raise MemoryError(f"session {sid}: no free batch or state slot")
+                if self.slots is not None:
+                    s.slot = self.slots.pop()
+                self.waiting.remove(s)
+                self.active.append(s)
+            need = self._blocks_needed(s, s.cached + n)
+            got = self.alloc.allocate(need) if need > 0 else []
+            if got is None:
+                raise MemoryError(f"session {sid}: {need} more blocks needed, {self.alloc.num_free} free")
+            s.blocks += got
+            s.step_tokens = n
+            batch.append(s)
+        return batch
+
+    def finish(self, session_id, reason="stop"):
+        """End a request from outside (an open-ended one, or one the caller no longer wants) and return what it holds."""
+        seq = self.sessions.get(session_id)
+        if seq is not None and not seq.finished:
+            seq.finished, seq.finish_reason = True, reason
+        if seq is not None and seq in self.waiting:
+            self.waiting.remove(seq)
+            self.sessions.pop(session_id, None)
+        self._retire()
 
     def schedule(self):
         """Form the batch of this step.  Returns the sequences that run; each feeds `step_tokens` tokens (1 unless it
@@ -303,6 +354,8 @@ class Scheduler:
                 self.waiting.popleft()
                 self.sessions.pop(s.session_id, None)
                 continue
+            if self.slots is not None and not self.slots:
+                break                      # every recurrent-state slot is held by a running sequence
             got = self.alloc.allocate(self._blocks_needed(s, upto))
             if got is None:
                 if self.prefix is not None:            # give the references back; retry from scratch next step
@@ -310,6 +363,8 @@ class Scheduler:
                     s.chain, s.cached, s.fed = [], 0, 0
                 break
             s.blocks += got
+            if self.slots is not None:
+                s.slot = self.slots.pop()
             self.waiting.popleft()
             self.active.append(s)
         batch = [s for s in self.active if not s.finished]
@@ -349,7 +404,7 @@ class Scheduler:
                         toks = [s.token_at(p) for p in range(j * bl, (j + 1) * bl)]
                         s.chain.append(prefix.publish(s.chain[-1] if s.chain else PrefixCache.ROOT, toks, s.blocks[j]))
             gen = s.generated
-            if cached < plen + len(gen):
+            if cached < plen + len(gen) or s.hold:
                 continue                   # still filling the cache (prompt, or refill after a preemption): sample discarded
             if s.max_new_tokens == 0:
                 s.finished, s.finish_reason = True, "length"

@@ -85,3 +85,135 @@ SPECS = {
     "llama3-70b": ModelSpec("llama3-70b", "llama", 8192, 80, 64, 8, 28672, 128256, 5e5, weight_format="fp8",
                             dtype="bf16"),
 }
+
+
+# ---------------------------------------------------------------------------------------------------- hybrid decoders
+# Decoders whose layers differ from one another: each layer names its sequence mixer (attention over a cached latent,
+# or a decayed linear-attention recurrence), its feed-forward (routed experts, or none) and their sizes; the per-layer
+# record is the whole description, so another stack of the same mechanisms is another list.
+
+@dataclass(frozen=True)
+class RotarySpec:
+    """Rotation of interleaved pairs (2i, 2i+1) of the first `dims` dimensions by position * f_i, f_i = base^(-2i/dims).
+    scaling = (factor, original, fast, slow) or None: frequencies are blended with f_i / factor along a ramp over the
+    pair index whose ends are the pairs that make `fast` and `slow` turns over `original` positions, and cos / sin grow
+    by 0.1 ln(factor) + 1 (the YaRN recipe)."""
+    dims: int
+    base: float
+    scaling: tuple = None
+
+    def frequencies(self):
+        """-> ([angle per position of pair i], factor on cos and sin), in double precision."""
+        import math
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)]
+        if self.scaling is None:
+            return f, 1.0
+        factor, original, fast, slow = self.scaling
+
+        def pair_of(turns):
+            return self.dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+
+        lo = max(math.floor(pair_of(fast)), 0)
+        hi = min(math.ceil(pair_of(slow)), self.dims - 1)
+        span = max(hi - lo, 0.001)
+        out = []
+        for i, fi in enumerate(f):
+            ramp = min(max((i - lo) / span, 0.0), 1.0)
+            out.append(fi / factor * ramp + fi * (1.0 - ramp))
+        return out, 0.1 * math.log(factor) + 1.0
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values are expanded from one cached latent per token, plus one rotated key part shared by
+    all heads; queries pass through a latent of their own; a learned per-head sink joins the softmax denominator."""
+    heads: int
+    dim: int            # unrotated query / key dimensions per head
+    rot_dim: int        # rotated ones
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    scale: float
+    rot: RotarySpec
+    kind = "latent_attention"
+
+
+@dataclass(frozen=True)
+class DecayAttentionSpec:
+    """Linear attention with a fixed decay per head: S <- decay_h S + k v^T, o = S^T q."""
+    heads: int
+    dim: int
+    vdim: int
+    decay: tuple
+    kind = "lightning"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    experts: int
+    top: int
+    ff: int
+
+
+@dataclass(frozen=True)
+class HybridLayerSpec:
+    mixer: object                       # LatentAttentionSpec | DecayAttentionSpec
+    mlp: RoutedExpertsSpec = None       # None: the layer has no feed-forward
+
+
+@dataclass(frozen=True)
+class HybridSpec:
+    name: str
+    arch: str
+    width: int
+    vocab: int
+    layers: tuple                       # of HybridLayerSpec
+    norm_eps: float
+    norm_groups: int
+    conv_taps: int
+    embedding_scale: float
+    dtype: str = "bf16"                 # 'bf16' | 'f32': the type of projections and their weights
+    session_len: int = 0
+    hybrid = True
+
+    @property
+    def hidden(self):
+        return self.width
+
+
+def _gulozen_mixer(kind, m):
+    if kind == "latent_attention":
+        r = m["rot"]
+        sc = r.get("scaling")
+        rot = RotarySpec(int(r["dims"]), float(r["base"]),
+                         None if not sc else (float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])))
+        if rot.dims > m["rot_dim"] or rot.dims % 2:
+            raise ValueError(f"rot.dims {rot.dims} does not fit rot_dim {m['rot_dim']}")
+        return LatentAttentionSpec(int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"]),
+                                   int(m["q_rank"]), float(m["scale"]), rot)
+    if kind == "lightning":
+        decay = tuple(float(d) for d in m["decay"])
+        if len(decay) != m["heads"]:
+            raise ValueError(f"{len(decay)} decays for {m['heads']} heads")
+        return DecayAttentionSpec(int(m["heads"]), int(m["dim"]), int(m["vdim"]), decay)
+    raise NotImplementedError(f"mixer type {kind!r}")
+
+
+def gulozen_spec(cfg, name="gulozen"):
+    """config.json of a Gulozen checkpoint -> HybridSpec.  Every size and constant is read from the config."""
+    layers = []
+    for entry in cfg["layers"]:
+        mlp = entry.get("mlp")
+        if mlp is not None:
+            if mlp.get("kind", "moe") != "moe":
+                raise NotImplementedError(f"feed-forward kind {mlp.get('kind')!r}")
+            mlp = RoutedExpertsSpec(int(mlp["router"]["experts"]), int(mlp["router"]["top"]), int(mlp["expert"]["ff"]))
+        layers.append(HybridLayerSpec(_gulozen_mixer(entry["type"], entry["mixer"]), mlp))
+    return HybridSpec(name=name, arch="gulozen", width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=tuple(layers),
+                      norm_eps=float(cfg["norm"]["eps"]), norm_groups=int(cfg["norm"]["groups"]),
+                      conv_taps=int(cfg["canon"]["taps"]), embedding_scale=float(cfg["embedding"]["scale"]),
+                      session_len=int(cfg.get("session_len", 0)))
+
+
+# config.json "architecture" -> spec builder, for checkpoints that are not HF `architectures` configs
+HYBRID_ARCHITECTURES = {"Gulozen": gulozen_spec}

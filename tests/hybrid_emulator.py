@@ -1,0 +1,192 @@
+"""A numpy stand-in for libb200hybrid.so that works on host memory -- TEST INFRASTRUCTURE ONLY.
+
+It has the entry points of include/b200_hybrid.h with the same argument lists and addresses rows, pages and state slots the
+way the header says, in float32 only (dtype B200H_F32), with the arithmetic written row by row in numpy.  With it the host
+side of a hybrid decoder (turbomind/hybrid.py, the engine, the scheduler's blocks and slots, bin/trace_run) runs without a
+GPU: a wrong page address, slot offset or row mapping shows on the CPU.  The CUDA kernels themselves are compared with
+oracle/gulozen.py on a device (tests/test_hybrid_gpu.py)."""
+import ctypes as C
+
+import numpy as np
+
+F32 = 2
+
+
+def _a(ptr, count, ctype=C.c_float):
+    if isinstance(ptr, C.c_void_p):
+        ptr = ptr.value
+    return np.ctypeslib.as_array(C.cast(int(ptr), C.POINTER(ctype)), shape=(int(count),))
+
+
+def _f(ptr, *shape):
+    return _a(ptr, int(np.prod(shape))).reshape(shape)
+
+
+def _i(ptr, count):
+    return _a(ptr, count, C.c_int)
+
+
+def _rows(ptr, n, ld, cols):
+    """[n, cols] view of a float matrix with row stride ld."""
+    return np.lib.stride_tricks.as_strided(_a(ptr, (n - 1) * ld + cols), (n, cols), (4 * ld, 4))
+
+
+def _unit(x, eps):
+    return x / np.sqrt((x * x).mean(-1, keepdims=True, dtype=np.float32) + np.float32(eps))
+
+
+def _sigmoid(z):
+    return 1.0 / (1.0 + np.exp(-z))
+
+
+class EmulatedHybridLib:
+    def b200h_last_error(self):
+        return b""
+
+    def b200h_embed(self, tokens, table, scale, out, n, width, dtype, stream):
+        assert dtype == F32
+        tok = _i(tokens, n)
+        tab = _a(table, (int(tok.max()) + 1) * width).reshape(-1, width)
+        _f(out, n, width)[:] = tab[tok] * np.float32(scale)
+        return 0
+
+    def b200h_causal_conv(self, x, w, state, slot_stride, tok_seq, cu_q, seq_slot, out, n, batch, width, taps, dtype, stream):
+        X, Wt, O = _f(x, n, width), _f(w, width, taps), _f(out, n, width)
+        cu, slots = _i(cu_q, batch + 1), _i(seq_slot, batch)
+        for s in range(batch):
+            lo, hi = cu[s], cu[s + 1]
+            if lo == hi:
+                continue
+            st = _f(int(state) + 4 * int(slots[s]) * slot_stride, taps - 1, width)
+            full = np.concatenate([st, X[lo:hi]], 0)
+            for t in range(hi - lo):
+                acc = X[lo + t].copy()
+                for j in range(taps):
+                    acc += Wt[:, j] * full[t + j]
+                O[lo + t] = acc
+            st[:] = full[full.shape[0] - (taps - 1):]
+        return 0
+
+    def b200h_residual_group_norm(self, x, m, m_is_f32, parts, w, n, width, groups, eps, x_t, dtype, stream):
+        X, M, Wn = _f(x, n, width), _f(m, n, parts, width), _f(w, width)
+        v = M[:, 0].copy()
+        for p in range(1, parts):
+            v += M[:, p]
+        y = _unit(v.reshape(n, groups, width // groups), eps).reshape(n, width) * Wn
+        X += y
+        if x_t:
+            _f(x_t, n, width)[:] = X
+        return 0
+
+    def b200h_group_norm_rows(self, x, rows, w, count, width, groups, eps, out, dtype, stream):
+        idx = _i(rows, count) if rows else np.arange(count)
+        X = _f(x, int(idx.max()) + 1, width)[idx]
+        _f(out, count, width)[:] = _unit(X.reshape(count, groups, width // groups), eps).reshape(count, width) * _f(w, width)
+        return 0
+
+    def b200h_depth_mix(self, x, hist, hist_stride, coef, terms, count, stream):
+        X, c = _a(x, count), _a(coef, terms)
+        Hs = [_a(int(hist) + 4 * j * hist_stride, count) for j in range(terms)]
+        Hs[terms - 1][:] = X
+        acc = np.zeros(count, np.float32)
+        for j in range(terms):
+            acc += c[j] * Hs[j]
+        X[:] = acc
+        return 0
+
+    @staticmethod
+    def _rot(v, pos, a):
+        f = _a(a.rot.freqs, a.rot.pairs, C.c_double)
+        ang = float(pos) * f
+        c, s = (np.cos(ang) * a.rot.magnitude).astype(np.float32), (np.sin(ang) * a.rot.magnitude).astype(np.float32)
+        out = v.copy()
+        u, w = v[..., 0:2 * a.rot.pairs:2], v[..., 1:2 * a.rot.pairs:2]
+        out[..., 0:2 * a.rot.pairs:2] = u * c - w * s
+        out[..., 1:2 * a.rot.pairs:2] = w * c + u * s
+        return out
+
+    @staticmethod
+    def _page(a, seq, pos):
+        cu = _i(a.cu_blocks, seq + 2)
+        ptrs = _a(a.block_ptrs, cu[seq + 1], C.c_int64)
+        base = int(ptrs[cu[seq] + pos // a.block_len]) + a.layer_off
+        at = pos % a.block_len
+        return _f(base + 4 * at * a.kv_rank, a.kv_rank), _f(base + a.rot_off + 4 * at * a.rot_dim, a.rot_dim)
+
+    def b200h_latent_prep(self, args):
+        a = args._obj
+        assert a.dtype == F32
+        dq, dkv = _rows(a.dq, a.n, a.ld_dq, a.q_rank), _rows(a.dkv, a.n, a.ld_dkv, a.kv_rank + a.rot_dim)
+        _f(a.cq, a.n, a.q_rank)[:] = _unit(dq, a.eps) * _f(a.q_norm, a.q_rank)
+        seqs, poss = _i(a.tok_seq, a.n), _i(a.tok_pos, a.n)
+        for t in range(a.n):
+            c, kr = self._page(a, int(seqs[t]), int(poss[t]))
+            c[:] = _unit(dkv[t, :a.kv_rank], a.eps) * _f(a.kv_norm, a.kv_rank)
+            kr[:] = self._rot(dkv[t, a.kv_rank:], poss[t], a)
+        return 0
+
+    def b200h_latent_attention(self, args):
+        a = args._obj
+        H, D, R, V, Ck = a.heads, a.dim, a.rot_dim, a.vdim, a.kv_rank
+        q = _rows(a.q, a.n, a.ld_q, H * (D + R)).reshape(a.n, H, D + R)
+        uk, uv, sink = _f(a.uk, H, D, Ck), _f(a.uv, H, V, Ck), _f(a.sink, H)
+        gate = _rows(a.gate, a.n, a.ld_gate, H * V)
+        y = _f(a.y, a.n, H * V)
+        seqs, poss = _i(a.tok_seq, a.n), _i(a.tok_pos, a.n)
+        for t in range(a.n):
+            s, pos = int(seqs[t]), int(poss[t])
+            cs, krs = zip(*[self._page(a, s, j) for j in range(pos + 1)])
+            cs, krs = np.stack(cs), np.stack(krs)
+            q_rot = self._rot(q[t, :, D:], pos, a) * np.float32(a.scale)
+            for h in range(H):
+                q_lat = (q[t, h, :D] @ uk[h]) * np.float32(a.scale)
+                sc = cs @ q_lat + krs @ q_rot[h]
+                top = max(float(sc.max()), float(sink[h]))
+                e = np.exp(sc - top)
+                o_lat = (e / (e.sum() + np.exp(sink[h] - top))) @ cs
+                y[t, h * V:(h + 1) * V] = (uv[h] @ o_lat) * _sigmoid(gate[t, h * V:(h + 1) * V])
+        return 0
+
+    def b200h_decay_attention(self, q, k, v, ld, decay, state, slot_stride, cu_q, seq_slot, batch, heads, dim, vdim, out, dtype, stream):
+        cu, slots, lam = _i(cu_q, batch + 1), _i(seq_slot, batch), _a(decay, heads)
+        n = int(cu[batch])
+        silu = lambda z: z * _sigmoid(z)
+        Q, K = silu(_rows(q, n, ld, heads * dim)).reshape(n, heads, dim), silu(_rows(k, n, ld, heads * dim)).reshape(n, heads, dim)
+        Vv = silu(_rows(v, n, ld, heads * vdim)).reshape(n, heads, vdim)
+        O = _f(out, n, heads, vdim)
+        for s in range(batch):
+            S = _f(int(state) + 4 * int(slots[s]) * slot_stride, heads, vdim, dim)
+            for t in range(cu[s], cu[s + 1]):
+                for h in range(heads):
+                    S[h] = lam[h] * S[h] + np.outer(Vv[t, h], K[t, h])
+                    O[t, h] = S[h] @ Q[t, h]
+        return 0
+
+    def b200h_gated_rms(self, o, w, gate, ld_gate, n, count, eps, y, dtype, stream):
+        _f(y, n, count)[:] = _unit(_f(o, n, count), eps) * _f(w, count) * _sigmoid(_rows(gate, n, ld_gate, count))
+        return 0
+
+    def b200h_route(self, x, router, n, width, experts, top, ids, wts, stream):
+        z = _f(x, n, width) @ _f(router, experts, width).T
+        e = np.exp(z - z.max(-1, keepdims=True))
+        sc = e / e.sum(-1, keepdims=True)
+        order = np.argsort(-sc, -1, kind="stable")[:, :top]
+        _i(ids, n * top).reshape(n, top)[:] = order
+        _f(wts, n, top)[:] = np.take_along_axis(sc, order, -1)
+        return 0
+
+    def b200h_experts(self, x, gate, up, down, ids, wts, n, width, ff, top, out, dtype, stream):
+        X, idx, wt = _f(x, n, width), _i(ids, n * top).reshape(n, top), _f(wts, n, top)
+        E = int(idx.max()) + 1
+        G, U, Dn = _f(gate, E, ff, width), _f(up, E, ff, width), _f(down, E, width, ff)
+        O = _f(out, n, top, width)
+        for t in range(n):
+            for k in range(top):
+                e = idx[t, k]
+                g = G[e] @ X[t]
+                O[t, k] = wt[t, k] * (Dn[e] @ (g * _sigmoid(g) * (U[e] @ X[t])))
+        return 0
+
+    def b200h_argmax(self, logits, ld, rows, vocab, out, stream):
+        _i(out, rows)[:] = _rows(logits, rows, ld, vocab).argmax(-1)
+        return 0
