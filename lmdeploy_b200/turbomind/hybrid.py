@@ -43,6 +43,13 @@ class StatePool:
         return self.storage.data_ptr() + 4 * float_offset
 
 
+class StepArrays:
+    """The device arrays every operator of a step addresses rows, pages and state through (see HybridModel.step)."""
+
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
 class HybridModel:
     """Weights of one hybrid decoder on one GPU and its step function."""
     kind = "hybrid"
@@ -220,70 +227,26 @@ class HybridModel:
         int32 [batch]; block_ptrs int64 (page addresses); rows int32 [n_rows] = the rows whose logits are wanted.
         Returns float logits [n_rows, vocab].  trace: a list that receives a copy of the stream after every layer."""
         s, lib, w, dev, T, dt = self.spec, self.lib, self.w, self.device, self.T, self.dt
-        W, eps, groups, taps = s.width, s.norm_eps, s.norm_groups, s.conv_taps
+        W, eps, groups = s.width, s.norm_eps, s.norm_groups
         st = self._stream()
-        L = len(s.layers)
+        c = StepArrays(n=n, batch=batch, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot, block_ptrs=block_ptrs,
+                       cu_blocks=cu_blocks, state=state)
         f32 = dict(dtype=torch.float32, device=dev)
-        hist = torch.empty(L + 1, n, W, **f32)
+        hist = torch.empty(len(s.layers) + 1, n, W, **f32)
         x = torch.empty(n, W, **f32)
         H.check(lib.b200h_embed(tokens.data_ptr(), w["embed"].data_ptr(), s.embedding_scale, hist.data_ptr(), n, W, dt, st), "embed")
         x.copy_(hist[0])
-        h = torch.empty(n, W, dtype=T, device=dev)
         xt = torch.empty(n, W, dtype=T, device=dev)
         for i, layer in enumerate(s.layers):
-            p, m = f"l{i}.", layer.mixer
-            H.check(lib.b200h_causal_conv(x.data_ptr(), w[p + "canon1"].data_ptr(), state.ptr(self.conv_off[i]), state.storage.stride(0),
-                                          tok_seq.data_ptr(), cu_q.data_ptr(), seq_slot.data_ptr(), h.data_ptr(), n, batch, W, taps,
-                                          dt, st), "causal_conv")
-            proj = self._linear(h, w[p + "in"])
-            ld, es = proj.stride(0), proj.element_size()
-            if m.kind == "latent_attention":
-                HV = m.heads * m.vdim
-                a = H.LatentArgs()
-                a.n, a.heads, a.dim, a.rot_dim, a.vdim, a.kv_rank, a.q_rank = n, m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
-                a.block_len, a.scale, a.eps = self.block_len, m.scale, eps
-                a.rot = H.Rotary(w[p + "freqs"].data_ptr(), m.rot.dims // 2, w[p + "mag"])
-                a.dq, a.ld_dq = proj.data_ptr(), ld
-                a.dkv, a.ld_dkv = proj.data_ptr() + es * m.q_rank, ld
-                a.gate, a.ld_gate = proj.data_ptr() + es * (m.q_rank + m.kv_rank + m.rot_dim), ld
-                a.q_norm, a.kv_norm, a.sink = w[p + "dq.norm"].data_ptr(), w[p + "dkv.norm"].data_ptr(), w[p + "sink"].data_ptr()
-                cq = torch.empty(n, m.q_rank, dtype=T, device=dev)
-                a.cq = cq.data_ptr()
-                a.tok_seq, a.tok_pos = tok_seq.data_ptr(), tok_pos.data_ptr()
-                a.block_ptrs, a.cu_blocks = block_ptrs.data_ptr(), cu_blocks.data_ptr()
-                a.layer_off, a.rot_off, a.dtype, a.stream = self.cache_off[i], self.rot_off[i], dt, st
-                H.check(lib.b200h_latent_prep(C.byref(a)), "latent_prep")
-                q = self._linear(cq, w[p + "uq"])
-                q_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
-                q_rot = torch.empty(n, m.heads, m.rot_dim, **f32)
-                o_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
-                y = torch.empty(n, HV, dtype=T, device=dev)
-                a.q, a.ld_q, a.uk, a.uv = q.data_ptr(), q.stride(0), w[p + "uk"].data_ptr(), w[p + "uv"].data_ptr()
-                a.q_lat, a.q_rot, a.o_lat, a.y = q_lat.data_ptr(), q_rot.data_ptr(), o_lat.data_ptr(), y.data_ptr()
-                H.check(lib.b200h_latent_attention(C.byref(a)), "latent_attention")
-            else:
-                HD, HV = m.heads * m.dim, m.heads * m.vdim
-                o = torch.empty(n, m.heads, m.vdim, **f32)
-                base = proj.data_ptr()
-                H.check(lib.b200h_decay_attention(base, base + es * HD, base + es * 2 * HD, ld, w[p + "decay"].data_ptr(),
-                                                  state.ptr(self.mix_off[i]), state.storage.stride(0), cu_q.data_ptr(),
-                                                  seq_slot.data_ptr(), batch, m.heads, m.dim, m.vdim, o.data_ptr(), dt, st),
-                        "decay_attention")
-                y = torch.empty(n, HV, dtype=T, device=dev)
-                H.check(lib.b200h_gated_rms(o.data_ptr(), w[p + "mixnorm"].data_ptr(), base + es * (2 * HD + HV), ld, n, HV, eps,
-                                            y.data_ptr(), dt, st), "gated_rms")
+            p = f"l{i}."
+            h = self.conv_input(i, x, c)
+            y = self.latent_mixer(i, h, c) if layer.mixer.kind == "latent_attention" else self.decay_mixer(i, h, c)
             mixed = self._linear(y, w[p + "o"])
             f = layer.mlp
             H.check(lib.b200h_residual_group_norm(x.data_ptr(), mixed.data_ptr(), 0, 1, w[p + "norm1"].data_ptr(), n, W, groups, eps,
                                                   xt.data_ptr() if f is not None else None, dt, st), "residual_group_norm")
             if f is not None:
-                ids = torch.empty(n, f.top, dtype=torch.int32, device=dev)
-                wts = torch.empty(n, f.top, **f32)
-                H.check(lib.b200h_route(x.data_ptr(), w[p + "router"].data_ptr(), n, W, f.experts, f.top, ids.data_ptr(), wts.data_ptr(), st),
-                        "route")
-                out = torch.empty(n, f.top, W, **f32)
-                H.check(lib.b200h_experts(xt.data_ptr(), w[p + "gate"].data_ptr(), w[p + "up"].data_ptr(), w[p + "down"].data_ptr(),
-                                          ids.data_ptr(), wts.data_ptr(), n, W, f.ff, f.top, out.data_ptr(), dt, st), "experts")
+                out = self.routed_experts(i, x, xt, n)
                 H.check(lib.b200h_residual_group_norm(x.data_ptr(), out.data_ptr(), 1, f.top, w[p + "norm2"].data_ptr(), n, W, groups, eps,
                                                       None, dt, st), "residual_group_norm")
             H.check(lib.b200h_depth_mix(x.data_ptr(), hist.data_ptr(), n * W, w[p + "dwa"].data_ptr(), i + 2, n * W, st), "depth_mix")
@@ -292,9 +255,93 @@ class HybridModel:
         xn = torch.empty(n_rows, W, dtype=T, device=dev)
         H.check(lib.b200h_group_norm_rows(x.data_ptr(), rows.data_ptr(), w["final.norm"].data_ptr(), n_rows, W, groups, eps, xn.data_ptr(),
                                           dt, st), "group_norm_rows")
-        if T is torch.float32:
-            return torch.mm(xn, w["head"].t())
-        return torch.mm(xn, w["head"].t(), out_dtype=torch.float32)
+        return self._logits(xn)
+
+    def _logits(self, xn):
+        """Float logits of normed rows: bf16 operands keep a float result (no rounding of the logits to bf16)."""
+        head = self.w["head"]
+        if self.T is torch.float32 or xn.device.type != "cuda":
+            return torch.mm(xn.float(), head.float().t())
+        try:
+            return torch.mm(xn, head.t(), out_dtype=torch.float32)
+        except RuntimeError:            # a shape the float-output GEMM refuses: float operands (same values, wider reads)
+            return torch.mm(xn.float(), head.float().t())
+
+    # ---- the mechanisms, one method each (the step above strings them together; tests call them alone)
+    def conv_input(self, i, x, c):
+        """What layer i's mixer reads: x + causal convolution of x over the sequence (as T); advances the layer's conv state."""
+        s, w = self.spec, self.w
+        h = torch.empty(c.n, s.width, dtype=self.T, device=self.device)
+        H.check(self.lib.b200h_causal_conv(x.data_ptr(), w[f"l{i}.canon1"].data_ptr(), c.state.ptr(self.conv_off[i]),
+                                           c.state.storage.stride(0), c.tok_seq.data_ptr(), c.cu_q.data_ptr(), c.seq_slot.data_ptr(),
+                                           h.data_ptr(), c.n, c.batch, s.width, s.conv_taps, self.dt, self._stream()), "causal_conv")
+        return h
+
+    def latent_mixer(self, i, h, c):
+        """Latent attention of layer i over rows h [n, width] (T): one stacked projection (query latent | key/value latent +
+        shared rotated key | gate), norms + rotation + cache store, query expansion, attention over the paged latents with the
+        sink, value expansion and gate.  Returns the gated heads [n, heads * vdim] (T), the output projection's input."""
+        m, w, lib, dev, T, n = self.spec.layers[i].mixer, self.w, self.lib, self.device, self.T, c.n
+        p = f"l{i}."
+        f32 = dict(dtype=torch.float32, device=dev)
+        proj = self._linear(h, w[p + "in"])
+        ld, es = proj.stride(0), proj.element_size()
+        a = H.LatentArgs()
+        a.n, a.heads, a.dim, a.rot_dim, a.vdim, a.kv_rank, a.q_rank = n, m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
+        a.block_len, a.scale, a.eps = self.block_len, m.scale, self.spec.norm_eps
+        a.rot = H.Rotary(w[p + "freqs"].data_ptr(), m.rot.dims // 2, w[p + "mag"])
+        a.dq, a.ld_dq = proj.data_ptr(), ld
+        a.dkv, a.ld_dkv = proj.data_ptr() + es * m.q_rank, ld
+        a.gate, a.ld_gate = proj.data_ptr() + es * (m.q_rank + m.kv_rank + m.rot_dim), ld
+        a.q_norm, a.kv_norm, a.sink = w[p + "dq.norm"].data_ptr(), w[p + "dkv.norm"].data_ptr(), w[p + "sink"].data_ptr()
+        cq = torch.empty(n, m.q_rank, dtype=T, device=dev)
+        a.cq = cq.data_ptr()
+        a.tok_seq, a.tok_pos = c.tok_seq.data_ptr(), c.tok_pos.data_ptr()
+        a.block_ptrs, a.cu_blocks = c.block_ptrs.data_ptr(), c.cu_blocks.data_ptr()
+        a.layer_off, a.rot_off, a.dtype, a.stream = self.cache_off[i], self.rot_off[i], self.dt, self._stream()
+        H.check(lib.b200h_latent_prep(C.byref(a)), "latent_prep")
+        q = self._linear(cq, w[p + "uq"])
+        q_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
+        q_rot = torch.empty(n, m.heads, m.rot_dim, **f32)
+        o_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
+        y = torch.empty(n, m.heads * m.vdim, dtype=T, device=dev)
+        a.q, a.ld_q, a.uk, a.uv = q.data_ptr(), q.stride(0), w[p + "uk"].data_ptr(), w[p + "uv"].data_ptr()
+        a.q_lat, a.q_rot, a.o_lat, a.y = q_lat.data_ptr(), q_rot.data_ptr(), o_lat.data_ptr(), y.data_ptr()
+        H.check(lib.b200h_latent_attention(C.byref(a)), "latent_attention")
+        return y
+
+    def decay_mixer(self, i, h, c):
+        """Decayed linear attention of layer i: one stacked projection (q | k | v | gate), the per-head recurrence on the
+        sequence's float state, then unit-rms norm over the concatenated heads times sigmoid(gate).  Returns [n, heads * vdim] (T)."""
+        m, w, lib, dev, n = self.spec.layers[i].mixer, self.w, self.lib, self.device, c.n
+        p = f"l{i}."
+        HD, HV = m.heads * m.dim, m.heads * m.vdim
+        proj = self._linear(h, w[p + "in"])
+        ld, es, base = proj.stride(0), proj.element_size(), proj.data_ptr()
+        o = torch.empty(n, m.heads, m.vdim, dtype=torch.float32, device=dev)
+        st = self._stream()
+        H.check(lib.b200h_decay_attention(base, base + es * HD, base + es * 2 * HD, ld, w[p + "decay"].data_ptr(),
+                                          c.state.ptr(self.mix_off[i]), c.state.storage.stride(0), c.cu_q.data_ptr(),
+                                          c.seq_slot.data_ptr(), c.batch, m.heads, m.dim, m.vdim, o.data_ptr(), self.dt, st),
+                "decay_attention")
+        y = torch.empty(n, HV, dtype=self.T, device=dev)
+        H.check(lib.b200h_gated_rms(o.data_ptr(), w[p + "mixnorm"].data_ptr(), base + es * (2 * HD + HV), ld, n, HV, self.spec.norm_eps,
+                                    y.data_ptr(), self.dt, st), "gated_rms")
+        return y
+
+    def routed_experts(self, i, x, xt, n):
+        """Routed experts of layer i: the router reads the float stream x, the experts its T copy xt.  Returns float
+        [n, top, width]: each chosen expert's output times its score (summed by the norm that follows)."""
+        f, w, lib, dev = self.spec.layers[i].mlp, self.w, self.lib, self.device
+        p, W, st = f"l{i}.", self.spec.width, self._stream()
+        ids = torch.empty(n, f.top, dtype=torch.int32, device=dev)
+        wts = torch.empty(n, f.top, dtype=torch.float32, device=dev)
+        H.check(lib.b200h_route(x.data_ptr(), w[p + "router"].data_ptr(), n, W, f.experts, f.top, ids.data_ptr(), wts.data_ptr(), st), "route")
+        out = torch.empty(n, f.top, W, dtype=torch.float32, device=dev)
+        H.check(lib.b200h_experts(xt.data_ptr(), w[p + "gate"].data_ptr(), w[p + "up"].data_ptr(), w[p + "down"].data_ptr(),
+                                  ids.data_ptr(), wts.data_ptr(), n, W, f.ff, f.top, out.data_ptr(), self.dt, st), "experts")
+        self.last_routing = (ids, wts)
+        return out
 
     def argmax(self, logits):
         """Greedy ids of float logits [r, vocab] (device int32 [r])."""

@@ -269,17 +269,18 @@ class Scheduler:
                 raise KeyError(f"session {sid} is not live")
             if n < 1 or s.cached + n > s.context_len:
                 raise ValueError(f"session {sid}: {n} tokens planned, {s.context_len - s.cached} available")
-            if s not in self.active:
-                if len(self.active) >= self.max_batch or (self.slots is not None and not self.slots):
-                    raise MemoryError(f"session {sid}: no free batch or state slot")
-                if self.slots is not None:
-                    s.slot = self.slots.pop()
-                self.waiting.remove(s)
-                self.active.append(s)
+            admit = s not in self.active
+            if admit and (len(self.active) >= self.max_batch or (self.slots is not None and not self.slots)):
+                raise MemoryError(f"session {sid}: no free batch or state slot")
             need = self._blocks_needed(s, s.cached + n)
             got = self.alloc.allocate(need) if need > 0 else []
             if got is None:
                 raise MemoryError(f"session {sid}: {need} more blocks needed, {self.alloc.num_free} free")
+            if admit:
+                if self.slots is not None:
+                    s.slot = self.slots.pop()
+                self.waiting.remove(s)
+                self.active.append(s)
             s.blocks += got
             s.step_tokens = n
             batch.append(s)

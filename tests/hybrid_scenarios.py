@@ -1,0 +1,122 @@
+"""Scenarios every hybrid-decoder engine must pass, whatever runs its operators: `make(cfg, tensors, **kw)` builds the engine
+(hybrid_cases.build_engine with a device, dtype and library chosen by the caller), `tol` bounds hybrid_cases.rel_error against
+the float64 oracle.  Run on the CPU through the numpy stand-in (tests/test_hybrid_cpu.py: host logic -- pages, slots, row
+addressing, scheduling) and on a GPU through the CUDA kernels (tests/test_hybrid_gpu.py)."""
+import numpy as np
+
+import hybrid_cases as HC
+
+
+def _check(got, want, tol, what):
+    err = HC.rel_error(got, want)
+    assert err.max() <= tol, f"{what}: relative error {err.max():.3g} at position {int(err.argmax())} (bound {tol})"
+
+
+def whole_prompt(make, tol):
+    cfg = HC.config()
+    w = HC.random_tensors(cfg)
+    P = HC.prompts_for(cfg, {"a": 70, "b": 1, "c": 5})
+    eng = make(cfg, w)
+    got = HC.replay(eng, P, [[("a", 70)], [("b", 1)], [("c", 5)]])
+    for k in P:
+        _check(got[k], HC.oracle_logits(cfg, w, P[k]), tol, f"whole prompt {k}")
+
+
+def prefill_then_decode(make, tol, n=140, tail=74):
+    """Most of a prompt in one step, the rest token by token across a page border (position 127 -> 128)."""
+    cfg = HC.config()
+    w = HC.random_tensors(cfg, seed=3)
+    P = HC.prompts_for(cfg, {"a": n})
+    eng = make(cfg, w)
+    got = HC.replay(eng, P, [[("a", n - tail)]] + [[("a", 1)]] * tail)
+    _check(got["a"], HC.oracle_logits(cfg, w, P["a"]), tol, "prefill then decode")
+
+
+def token_by_token(make, tol, n=68):
+    """Every token alone from the first: the first tokens of a sequence meet an empty conv state, an empty recurrent state
+    and a cache with nothing but the sink."""
+    cfg = HC.config()
+    w = HC.random_tensors(cfg, seed=4)
+    P = HC.prompts_for(cfg, {"a": n})
+    got = HC.replay(make(cfg, w), P, [[("a", 1)]] * n)
+    _check(got["a"], HC.oracle_logits(cfg, w, P["a"]), tol, "token by token")
+
+
+def portions(make, tol):
+    """Portions of several sizes down to two tokens (shorter than the convolution), cut inside pages and at their borders."""
+    cfg = HC.config(taps=4)
+    w = HC.random_tensors(cfg, seed=5)
+    cuts = [2, 3, 1, 2, 56, 2, 1, 61, 2, 64, 5]          # borders of the 64-token pages fall inside and between portions
+    P = HC.prompts_for(cfg, {"a": sum(cuts)})
+    got = HC.replay(make(cfg, w), P, [[("a", c)] for c in cuts])
+    _check(got["a"], HC.oracle_logits(cfg, w, P["a"]), tol, "portions")
+
+
+def unequal_batch(make, tol):
+    """Requests of unequal length in one batch -- portions beside single tokens -- against each alone."""
+    cfg = HC.config()
+    w = HC.random_tensors(cfg, seed=6)
+    P = HC.prompts_for(cfg, {"a": 90, "b": 7, "c": 66, "d": 2})
+    sched = [[("a", 30), ("b", 3)], [("b", 1), ("c", 64), ("a", 2)], [("a", 50), ("d", 2), ("c", 1), ("b", 1)],
+             [("c", 1), ("a", 1), ("b", 2)], [("a", 7)]]
+    got = HC.replay(make(cfg, w), P, sched)
+    for k in P:
+        _check(got[k], HC.oracle_logits(cfg, w, P[k]), tol, f"batched {k}")
+
+
+def reuse_of_pages_and_slots(make, tol):
+    """A pool of 3 pages and 2 state slots serves five requests one after another and side by side: every page and slot is
+    handed out again, and a request repeated in a used slot gives what it gave in a fresh one."""
+    cfg = HC.config()
+    w = HC.random_tensors(cfg, seed=7)
+    P = HC.prompts_for(cfg, {"a": 100, "b": 20, "c": 64})
+    eng = make(cfg, w, blocks=3, max_batch=2)
+    sched = [[("a", 64), ("b", 20)], [("a", 36), ("c", 10)], [("c", 54), ("b#2", 5)], [("b#2", 15), ("a#2", 30)], [("a#2", 70)],
+             [("c#2", 64), ("b#3", 20)]]
+    got = HC.replay(eng, P, sched)
+    assert eng.scheduler.alloc.num_free == 3 and sorted(eng.scheduler.slots) == [0, 1]
+    for k, v in got.items():
+        _check(v, HC.oracle_logits(cfg, w, P[k.split("#")[0]]), tol, f"reuse {k}")
+
+
+def other_sizes(make, tol):
+    """Sizes that a given model may make equal or 1: one norm group, no convolution history (taps 1), one head, every expert
+    chosen, a single expert, rot.dims below rot_dim, no rotary scaling, a decay of exactly 1, a lone layer."""
+    stacks = [
+        dict(layers=[dict(HC.latent(heads=1, dim=4, rot_dim=6, rot_dims=2, vdim=3, kv_rank=5, q_rank=3), mlp=HC.moe(experts=1, top=1, ff=4))],
+             width=16, groups=1, taps=1, vocab=9),
+        dict(layers=[dict(HC.lightning(heads=1, dim=33, vdim=9, decay=(1.0,)), mlp=None),
+                     dict(HC.latent(heads=5, dim=16, rot_dim=16, rot_dims=16, vdim=16, kv_rank=40, q_rank=16, scaling=False),
+                          mlp=HC.moe(experts=6, top=6, ff=10))], width=40, groups=4, taps=5, vocab=33),
+    ]
+    for k, kw in enumerate(stacks):
+        cfg = HC.config(**kw)
+        w = HC.random_tensors(cfg, seed=10 + k)
+        P = HC.prompts_for(cfg, {"a": 67})
+        got = HC.replay(make(cfg, w), P, [[("a", 3)], [("a", 62)], [("a", 1)], [("a", 1)]])
+        _check(got["a"], HC.oracle_logits(cfg, w, P["a"]), tol, f"sizes {k}")
+
+
+def greedy_generation(make, tol, new=10):
+    """batched_generate (the scheduler's own admission, chunking and retirement, greedy sampling on the device) against the
+    oracle generating greedily; a position whose two best oracle logits are closer than the tolerance may differ."""
+    from lmdeploy_b200.messages import GenerationConfig
+    from lmdeploy_b200.turbomind.engine import batched_generate
+    cfg = HC.config()
+    w = HC.random_tensors(cfg, seed=8)
+    P = HC.prompts_for(cfg, {"a": 9, "b": 70, "c": 1})
+    eng = make(cfg, w, blocks=4, max_batch=2, prefill_tokens=32)       # prompts longer than a step's token budget are chunked
+    seqs = batched_generate(eng, [P[k] for k in "abc"], GenerationConfig(max_new_tokens=new, ignore_eos=True))
+    assert eng.scheduler.alloc.num_free == 4 and sorted(eng.scheduler.slots) == [0, 1]
+    for k, s in zip("abc", seqs):
+        assert len(s.generated) == new and s.finish_reason == "length"
+        toks = list(P[k])
+        for i, t in enumerate(s.generated):
+            lg = HC.oracle_logits(cfg, w, toks)[-1]
+            best = np.sort(lg)[::-1]
+            if int(lg.argmax()) != t:
+                assert best[0] - lg[t] <= 4 * tol * np.abs(lg).max(), f"{k}: token {i} is {t}, oracle {int(lg.argmax())}"
+            toks.append(t)
+
+
+ALL = [whole_prompt, prefill_then_decode, token_by_token, portions, unequal_batch, reuse_of_pages_and_slots, other_sizes, greedy_generation]
