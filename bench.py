@@ -42,6 +42,120 @@ MIN_GPUS = {"c5": 2}
 WEIGHT_LABEL = {"awq": "W4A16", "fp16": "fp16", "fp8": "FP8"}
 
 
+# --hybrid: layer sizes of the order of deployed latent-attention / linear-attention / routed-expert models, and the dense
+# (GQA + gated FFN) geometry with the same width, head count and ACTIVE feed-forward size (top * ff == inter)
+HYBRID_SIZES = {
+    "w2048": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, experts=8, top=2, ff=2048,
+                  dense=dict(hidden=2048, heads=16, kv_heads=8, inter=4096)),
+    "w4096": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536, experts=8, top=2, ff=4096,
+                  dense=dict(hidden=4096, heads=32, kv_heads=8, inter=8192)),
+}
+HYBRID_VOCAB, HYBRID_LAYERS = 32000, ("latent_attention", "latent_attention", "lightning", "latent_attention")
+
+
+def hybrid_config(z):
+    """A Gulozen config.json (dict) of size `z`: three latent-attention layers and one decayed-linear-attention layer, each
+    with routed experts."""
+    rot = {"dims": z["rot_dim"], "base": 10000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    lat = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+           "q_rank": z["q_rank"], "scale": (z["dim"] + z["rot_dim"]) ** -0.5, "rot": rot}
+    lin = {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "decay": [1.0 - 2.0 ** -(3 + 5 * h / z["heads"]) for h in range(z["heads"])]}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    return {"architecture": "Gulozen", "canon": {"taps": 4}, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6, "groups": 2},
+            "vocab": HYBRID_VOCAB, "width": z["width"],
+            "layers": [{"type": t, "mixer": lat if t == "latent_attention" else lin, "mlp": mlp} for t in HYBRID_LAYERS]}
+
+
+def _engine_throughput(torch, eng, vocab, batch, ctx, steps, warm):
+    """Prompts of `ctx` tokens for `batch` requests through TurboMind.step: tokens/s of prompt ingestion (until every request
+    has produced its first token) and of `steps` decode steps after `warm` untimed ones.  Wall clock around synchronised
+    device work: scheduler, marshalling, H2D / D2H included."""
+    import numpy as np
+    from lmdeploy_b200.messages import GenerationConfig
+    from lmdeploy_b200.turbomind.engine import TurboMindInstance
+    inst = TurboMindInstance(eng)
+    rng = np.random.default_rng(0)
+    gen = GenerationConfig(max_new_tokens=warm + steps + 4, ignore_eos=True)
+    seqs = [inst._submit(eng.new_session_id(), rng.integers(0, vocab, ctx).tolist(), gen) for _ in range(batch)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ticks = 0
+    while not all(s.generated for s in seqs):
+        eng.step()
+        ticks += 1
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    for _ in range(warm):
+        eng.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    tokens = 0
+    for _ in range(steps):
+        tokens += sum(1 for _, tok in eng.step() if tok is not None)
+    torch.cuda.synchronize()
+    decode_s = time.perf_counter() - t0
+    assert tokens == batch * steps, (tokens, batch, steps)
+    return dict(prefill_tokens_per_s=batch * ctx / prefill_s, prefill_steps=ticks, decode_tokens_per_s=tokens / decode_s,
+                decode_ms_per_step=decode_s / steps * 1e3), seqs
+
+
+def run_hybrid(args):
+    """--hybrid SIZE: the hybrid decoder and the dense decoder of equal size, each through its engine, same batch and context."""
+    import torch
+    from lmdeploy_b200.messages import TurbomindEngineConfig
+    from lmdeploy_b200.turbomind import ModelSpec
+    from lmdeploy_b200.turbomind.engine import TurboMind
+    from lmdeploy_b200.turbomind.specs import gulozen_spec
+    z = HYBRID_SIZES[args.hybrid]
+    batch, ctx, steps, warm = args.hybrid_batch, args.hybrid_ctx, args.steps, max(args.warmup, 3)
+    session = ctx + warm + steps + 8
+    blocks = batch * ((session + 63) // 64) + 4
+    out = {"metric": "hybrid_vs_dense_tokens_per_s", "size": args.hybrid, "batch": batch, "ctx": ctx, "steps": steps, "warmup": warm,
+           "dtype": "bf16 (hybrid) / f16 (dense)", "data": "synthetic", "layers": len(HYBRID_LAYERS)}
+    with ClockSampler() as clocks:
+        clocks.wait_ready()
+        spec = gulozen_spec(hybrid_config(z), name=f"gulozen-{args.hybrid}")
+        eng = TurboMind(spec, TurbomindEngineConfig(dtype="bfloat16", max_batch_size=batch, session_len=session, cache_max_entry_count=blocks,
+                                                    max_prefill_token_num=8192), seed=0)
+        out["hybrid"], seqs = _engine_throughput(torch, eng, HYBRID_VOCAB, batch, ctx, steps, warm)
+        out["hybrid"]["weight_bytes"] = eng.model.weight_bytes
+        # per-operator device time: eight more decode steps, then one fresh 4096-row prefill step, bracketed by CUDA events
+        eng.model.events = []
+        for _ in range(8):
+            eng.step()
+        out["hybrid"]["decode_operator_ms_per_step"] = {k: round(v / 8, 4) for k, v in eng.model.operator_ms().items()}
+        for s in seqs:
+            eng.scheduler.finish(s.session_id)
+        _engine_prefill_once(torch, eng, HYBRID_VOCAB, 4, 1024)
+        eng.model.operator_ms()
+        _engine_prefill_once(torch, eng, HYBRID_VOCAB, 4, 1024)
+        out["hybrid"]["prefill_4x1024_operator_ms"] = {k: round(v, 4) for k, v in eng.model.operator_ms().items()}
+        del eng
+        torch.cuda.empty_cache()
+        d = z["dense"]
+        dspec = ModelSpec(f"dense-{args.hybrid}", "llama", d["hidden"], len(HYBRID_LAYERS), d["heads"], d["kv_heads"], d["inter"], HYBRID_VOCAB,
+                          1e4, weight_format="fp16")
+        deng = TurboMind(dspec, TurbomindEngineConfig(max_batch_size=batch, session_len=session, cache_max_entry_count=blocks, quant_policy=0),
+                         seed=0)
+        out["dense"], _ = _engine_throughput(torch, deng, HYBRID_VOCAB, batch, ctx, steps, warm)
+        out["dense"]["weight_bytes"] = deng.model.weight_bytes + deng.model.lm_head_bytes
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+
+
+def _engine_prefill_once(torch, eng, vocab, batch, ctx):
+    import numpy as np
+    from lmdeploy_b200.messages import GenerationConfig
+    from lmdeploy_b200.turbomind.engine import TurboMindInstance
+    inst = TurboMindInstance(eng)
+    rng = np.random.default_rng(1)
+    seqs = [inst._submit(eng.new_session_id(), rng.integers(0, vocab, ctx).tolist(), GenerationConfig(max_new_tokens=1, ignore_eos=True))
+            for _ in range(batch)]
+    while not all(s.finished for s in seqs):
+        eng.step()
+    torch.cuda.synchronize()
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -49,6 +163,11 @@ def parse():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", default="c2", choices=list(CONFIGS))
+    ap.add_argument("--hybrid", default=None, choices=list(HYBRID_SIZES),
+                    help="instead of the default workload: prefill and decode tokens/s of a Gulozen hybrid decoder of this size "
+                         "beside the dense decoder of equal size, both through the engine (random weights)")
+    ap.add_argument("--hybrid-batch", type=int, default=32)
+    ap.add_argument("--hybrid-ctx", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true", help="do not capture the step in a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--attn-iters", type=int, default=20)
@@ -478,6 +597,8 @@ def run_b200(args):
 
 def main():
     args = parse()
+    if args.hybrid:
+        return run_hybrid(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -12,6 +12,7 @@ Compute: every operator except the plain matrix products is a kernel of libb200h
 plain projections are cuBLAS GEMMs through torch (bf16 with float accumulation, or true float32 with TF32 off).  What the
 design wants in 32 bits (residual stream and its history, norms, rotary angles, scores, softmax, recurrent state, router)
 is float in every kernel whatever the projection type is."""
+import contextlib
 import ctypes as C
 
 import torch
@@ -97,6 +98,7 @@ class HybridModel:
         self.slot_floats = slot
         self.w = {}
         self.weight_bytes = 0
+        self.events = None          # a list while profiling: (operator, start event, end event) of every timed region
         if spec.dtype == "f32":
             # float32 serving means true 32-bit products: no TF32, no reduced-precision accumulation
             torch.backends.cuda.matmul.allow_tf32 = False
@@ -215,6 +217,27 @@ class HybridModel:
         return out
 
     # ------------------------------------------------------------------ step
+    @contextlib.contextmanager
+    def timed(self, name):
+        """Bracket an operator with CUDA events while profiling (bench.py); free otherwise."""
+        if self.events is None:
+            yield
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        yield
+        b.record()
+        self.events.append((name, a, b))
+
+    def operator_ms(self):
+        """Profiling: total milliseconds per operator since `events` was last cleared."""
+        torch.cuda.synchronize(self.device)
+        out = {}
+        for name, a, b in self.events:
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        self.events = []
+        return out
+
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream if self.device.type == "cuda" else None
 
@@ -234,28 +257,34 @@ class HybridModel:
         f32 = dict(dtype=torch.float32, device=dev)
         hist = torch.empty(len(s.layers) + 1, n, W, **f32)
         x = torch.empty(n, W, **f32)
-        H.check(lib.b200h_embed(tokens.data_ptr(), w["embed"].data_ptr(), s.embedding_scale, hist.data_ptr(), n, W, dt, st), "embed")
-        x.copy_(hist[0])
+        with self.timed("embed"):
+            H.check(lib.b200h_embed(tokens.data_ptr(), w["embed"].data_ptr(), s.embedding_scale, hist.data_ptr(), n, W, dt, st), "embed")
+            x.copy_(hist[0])
         xt = torch.empty(n, W, dtype=T, device=dev)
         for i, layer in enumerate(s.layers):
             p = f"l{i}."
             h = self.conv_input(i, x, c)
             y = self.latent_mixer(i, h, c) if layer.mixer.kind == "latent_attention" else self.decay_mixer(i, h, c)
-            mixed = self._linear(y, w[p + "o"])
+            with self.timed("gemm out"):
+                mixed = self._linear(y, w[p + "o"])
             f = layer.mlp
-            H.check(lib.b200h_residual_group_norm(x.data_ptr(), mixed.data_ptr(), 0, 1, w[p + "norm1"].data_ptr(), n, W, groups, eps,
-                                                  xt.data_ptr() if f is not None else None, dt, st), "residual_group_norm")
+            with self.timed("residual + grouped norm"):
+                H.check(lib.b200h_residual_group_norm(x.data_ptr(), mixed.data_ptr(), 0, 1, w[p + "norm1"].data_ptr(), n, W, groups, eps,
+                                                      xt.data_ptr() if f is not None else None, dt, st), "residual_group_norm")
             if f is not None:
                 out = self.routed_experts(i, x, xt, n)
-                H.check(lib.b200h_residual_group_norm(x.data_ptr(), out.data_ptr(), 1, f.top, w[p + "norm2"].data_ptr(), n, W, groups, eps,
-                                                      None, dt, st), "residual_group_norm")
-            H.check(lib.b200h_depth_mix(x.data_ptr(), hist.data_ptr(), n * W, w[p + "dwa"].data_ptr(), i + 2, n * W, st), "depth_mix")
+                with self.timed("residual + grouped norm"):
+                    H.check(lib.b200h_residual_group_norm(x.data_ptr(), out.data_ptr(), 1, f.top, w[p + "norm2"].data_ptr(), n, W, groups,
+                                                          eps, None, dt, st), "residual_group_norm")
+            with self.timed("depth mix"):
+                H.check(lib.b200h_depth_mix(x.data_ptr(), hist.data_ptr(), n * W, w[p + "dwa"].data_ptr(), i + 2, n * W, st), "depth_mix")
             if trace is not None:
                 trace.append(x.clone())
         xn = torch.empty(n_rows, W, dtype=T, device=dev)
-        H.check(lib.b200h_group_norm_rows(x.data_ptr(), rows.data_ptr(), w["final.norm"].data_ptr(), n_rows, W, groups, eps, xn.data_ptr(),
-                                          dt, st), "group_norm_rows")
-        return self._logits(xn)
+        with self.timed("final norm + head"):
+            H.check(lib.b200h_group_norm_rows(x.data_ptr(), rows.data_ptr(), w["final.norm"].data_ptr(), n_rows, W, groups, eps,
+                                              xn.data_ptr(), dt, st), "group_norm_rows")
+            return self._logits(xn)
 
     def _logits(self, xn):
         """Float logits of normed rows: bf16 operands keep a float result (no rounding of the logits to bf16)."""
@@ -272,9 +301,10 @@ class HybridModel:
         """What layer i's mixer reads: x + causal convolution of x over the sequence (as T); advances the layer's conv state."""
         s, w = self.spec, self.w
         h = torch.empty(c.n, s.width, dtype=self.T, device=self.device)
-        H.check(self.lib.b200h_causal_conv(x.data_ptr(), w[f"l{i}.canon1"].data_ptr(), c.state.ptr(self.conv_off[i]),
-                                           c.state.storage.stride(0), c.tok_seq.data_ptr(), c.cu_q.data_ptr(), c.seq_slot.data_ptr(),
-                                           h.data_ptr(), c.n, c.batch, s.width, s.conv_taps, self.dt, self._stream()), "causal_conv")
+        with self.timed("causal conv"):
+            H.check(self.lib.b200h_causal_conv(x.data_ptr(), w[f"l{i}.canon1"].data_ptr(), c.state.ptr(self.conv_off[i]),
+                                               c.state.storage.stride(0), c.tok_seq.data_ptr(), c.cu_q.data_ptr(), c.seq_slot.data_ptr(),
+                                               h.data_ptr(), c.n, c.batch, s.width, s.conv_taps, self.dt, self._stream()), "causal_conv")
         return h
 
     def latent_mixer(self, i, h, c):
@@ -284,7 +314,8 @@ class HybridModel:
         m, w, lib, dev, T, n = self.spec.layers[i].mixer, self.w, self.lib, self.device, self.T, c.n
         p = f"l{i}."
         f32 = dict(dtype=torch.float32, device=dev)
-        proj = self._linear(h, w[p + "in"])
+        with self.timed("gemm in"):
+            proj = self._linear(h, w[p + "in"])
         ld, es = proj.stride(0), proj.element_size()
         a = H.LatentArgs()
         a.n, a.heads, a.dim, a.rot_dim, a.vdim, a.kv_rank, a.q_rank = n, m.heads, m.dim, m.rot_dim, m.vdim, m.kv_rank, m.q_rank
@@ -299,15 +330,18 @@ class HybridModel:
         a.tok_seq, a.tok_pos = c.tok_seq.data_ptr(), c.tok_pos.data_ptr()
         a.block_ptrs, a.cu_blocks = c.block_ptrs.data_ptr(), c.cu_blocks.data_ptr()
         a.layer_off, a.rot_off, a.dtype, a.stream = self.cache_off[i], self.rot_off[i], self.dt, self._stream()
-        H.check(lib.b200h_latent_prep(C.byref(a)), "latent_prep")
-        q = self._linear(cq, w[p + "uq"])
+        with self.timed("latent norm + rotate + cache store"):
+            H.check(lib.b200h_latent_prep(C.byref(a)), "latent_prep")
+        with self.timed("gemm query up"):
+            q = self._linear(cq, w[p + "uq"])
         q_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
         q_rot = torch.empty(n, m.heads, m.rot_dim, **f32)
         o_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
         y = torch.empty(n, m.heads * m.vdim, dtype=T, device=dev)
         a.q, a.ld_q, a.uk, a.uv = q.data_ptr(), q.stride(0), w[p + "uk"].data_ptr(), w[p + "uv"].data_ptr()
         a.q_lat, a.q_rot, a.o_lat, a.y = q_lat.data_ptr(), q_rot.data_ptr(), o_lat.data_ptr(), y.data_ptr()
-        H.check(lib.b200h_latent_attention(C.byref(a)), "latent_attention")
+        with self.timed("latent attention"):
+            H.check(lib.b200h_latent_attention(C.byref(a)), "latent_attention")
         return y
 
     def decay_mixer(self, i, h, c):
@@ -316,17 +350,20 @@ class HybridModel:
         m, w, lib, dev, n = self.spec.layers[i].mixer, self.w, self.lib, self.device, c.n
         p = f"l{i}."
         HD, HV = m.heads * m.dim, m.heads * m.vdim
-        proj = self._linear(h, w[p + "in"])
+        with self.timed("gemm in"):
+            proj = self._linear(h, w[p + "in"])
         ld, es, base = proj.stride(0), proj.element_size(), proj.data_ptr()
         o = torch.empty(n, m.heads, m.vdim, dtype=torch.float32, device=dev)
         st = self._stream()
-        H.check(lib.b200h_decay_attention(base, base + es * HD, base + es * 2 * HD, ld, w[p + "decay"].data_ptr(),
-                                          c.state.ptr(self.mix_off[i]), c.state.storage.stride(0), c.cu_q.data_ptr(),
-                                          c.seq_slot.data_ptr(), c.batch, m.heads, m.dim, m.vdim, o.data_ptr(), self.dt, st),
-                "decay_attention")
+        with self.timed("decayed linear attention"):
+            H.check(lib.b200h_decay_attention(base, base + es * HD, base + es * 2 * HD, ld, w[p + "decay"].data_ptr(),
+                                              c.state.ptr(self.mix_off[i]), c.state.storage.stride(0), c.cu_q.data_ptr(),
+                                              c.seq_slot.data_ptr(), c.batch, m.heads, m.dim, m.vdim, o.data_ptr(), self.dt, st),
+                    "decay_attention")
         y = torch.empty(n, HV, dtype=self.T, device=dev)
-        H.check(lib.b200h_gated_rms(o.data_ptr(), w[p + "mixnorm"].data_ptr(), base + es * (2 * HD + HV), ld, n, HV, self.spec.norm_eps,
-                                    y.data_ptr(), self.dt, st), "gated_rms")
+        with self.timed("gated unit norm"):
+            H.check(lib.b200h_gated_rms(o.data_ptr(), w[p + "mixnorm"].data_ptr(), base + es * (2 * HD + HV), ld, n, HV, self.spec.norm_eps,
+                                        y.data_ptr(), self.dt, st), "gated_rms")
         return y
 
     def routed_experts(self, i, x, xt, n):
@@ -336,10 +373,13 @@ class HybridModel:
         p, W, st = f"l{i}.", self.spec.width, self._stream()
         ids = torch.empty(n, f.top, dtype=torch.int32, device=dev)
         wts = torch.empty(n, f.top, dtype=torch.float32, device=dev)
-        H.check(lib.b200h_route(x.data_ptr(), w[p + "router"].data_ptr(), n, W, f.experts, f.top, ids.data_ptr(), wts.data_ptr(), st), "route")
+        with self.timed("router"):
+            H.check(lib.b200h_route(x.data_ptr(), w[p + "router"].data_ptr(), n, W, f.experts, f.top, ids.data_ptr(), wts.data_ptr(), st),
+                    "route")
         out = torch.empty(n, f.top, W, dtype=torch.float32, device=dev)
-        H.check(lib.b200h_experts(xt.data_ptr(), w[p + "gate"].data_ptr(), w[p + "up"].data_ptr(), w[p + "down"].data_ptr(),
-                                  ids.data_ptr(), wts.data_ptr(), n, W, f.ff, f.top, out.data_ptr(), self.dt, st), "experts")
+        with self.timed("experts"):
+            H.check(lib.b200h_experts(xt.data_ptr(), w[p + "gate"].data_ptr(), w[p + "up"].data_ptr(), w[p + "down"].data_ptr(),
+                                      ids.data_ptr(), wts.data_ptr(), n, W, f.ff, f.top, out.data_ptr(), self.dt, st), "experts")
         self.last_routing = (ids, wts)
         return out
 

@@ -179,7 +179,7 @@ def test_routed_experts_take_the_largest_scores_unrenormalised(experts, top, dty
     scores = torch.softmax(x.double() @ p["router"].T, -1)
     assert (ids.cpu().long() == scores.topk(top, -1).indices).all()
     _close(wts.cpu(), scores.topk(top, -1).values, 1e-5, "router weights")
-    assert top == experts or float(wts.sum(-1).max()) < 1.0          # the chosen scores are not renormalised
+    assert top == experts or float(wts.sum(-1).min()) < 0.999        # the chosen scores are not renormalised
 
 
 def test_argmax_takes_the_lowest_index_of_equal_logits():
