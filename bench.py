@@ -75,7 +75,8 @@ def _engine_throughput(torch, eng, vocab, batch, ctx, steps, warm):
     from lmdeploy_b200.turbomind.engine import TurboMindInstance
     inst = TurboMindInstance(eng)
     rng = np.random.default_rng(0)
-    gen = GenerationConfig(max_new_tokens=warm + steps + 4, ignore_eos=True)
+    # requests that finish their prompt early decode while the others are still being ingested: leave them room
+    gen = GenerationConfig(max_new_tokens=ctx + warm + steps + 4, ignore_eos=True)
     seqs = [inst._submit(eng.new_session_id(), rng.integers(0, vocab, ctx).tolist(), gen) for _ in range(batch)]
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -108,7 +109,7 @@ def run_hybrid(args):
     from lmdeploy_b200.turbomind.specs import gulozen_spec
     z = HYBRID_SIZES[args.hybrid]
     batch, ctx, steps, warm = args.hybrid_batch, args.hybrid_ctx, args.steps, max(args.warmup, 3)
-    session = ctx + warm + steps + 8
+    session = 2 * ctx + warm + steps + 16
     blocks = batch * ((session + 63) // 64) + 4
     out = {"metric": "hybrid_vs_dense_tokens_per_s", "size": args.hybrid, "batch": batch, "ctx": ctx, "steps": steps, "warmup": warm,
            "dtype": "bf16 (hybrid) / f16 (dense)", "data": "synthetic", "layers": len(HYBRID_LAYERS)}

@@ -55,7 +55,9 @@ typedef struct b200h_latent_args {
     int64_t ld_gate;
     void* q_lat;             /* float [n, heads, kv_rank] scratch */
     void* q_rot;             /* float [n, heads, rot_dim] scratch */
-    void* o_lat;             /* float [n, heads, kv_rank] scratch */
+    void* o_lat;             /* float [n, heads, splits, kv_rank] scratch: unnormalised partial of every key range */
+    void* ml;                /* float [n, heads, splits, 2] scratch: running maximum and denominator of every key range */
+    int splits;              /* key ranges per row (whole pages each), >= 1 */
     void* y;                 /* T [n, heads * vdim]: gated heads, the output projection's input */
     const void* tok_seq;     /* int [n] */
     const void* tok_pos;     /* int [n] */
@@ -109,6 +111,14 @@ B200H_API int b200h_route(const void* x, const void* router, int n, int width, i
  * out float [n, top, width]. */
 B200H_API int b200h_experts(const void* x, const void* gate, const void* up, const void* down, const void* ids, const void* wts, int n,
                             int width, int ff, int top, void* out, int dtype, void* stream);
+
+/* out = silu(g) * u element by element (T, `count` elements): between an expert's gate / up GEMMs and its down GEMM. */
+B200H_API int b200h_silu_mul(const void* g, const void* u, void* out, int64_t count, int dtype, void* stream);
+
+/* out[slot[r]] = wts[slot[r]] * src[r]: rows grouped by expert (src T [rows, width]) back to their (row, choice) places
+ * (out float [rows, width], wts float [rows], slot int [rows]). */
+B200H_API int b200h_weighted_scatter(const void* src, const void* slot, const void* wts, void* out, int rows, int width, int dtype,
+                                     void* stream);
 
 /* out[r] = index of the largest of logits[r, :vocab] (float, row stride ld; ties: the lowest index). */
 B200H_API int b200h_argmax(const void* logits, int64_t ld, int rows, int vocab, void* out, void* stream);

@@ -22,7 +22,8 @@ class LatentArgs(C.Structure):
         ("q_norm", C.c_void_p), ("kv_norm", C.c_void_p), ("cq", C.c_void_p),
         ("q", C.c_void_p), ("ld_q", C.c_int64), ("uk", C.c_void_p), ("uv", C.c_void_p), ("sink", C.c_void_p),
         ("gate", C.c_void_p), ("ld_gate", C.c_int64),
-        ("q_lat", C.c_void_p), ("q_rot", C.c_void_p), ("o_lat", C.c_void_p), ("y", C.c_void_p),
+        ("q_lat", C.c_void_p), ("q_rot", C.c_void_p), ("o_lat", C.c_void_p), ("ml", C.c_void_p), ("splits", C.c_int),
+        ("y", C.c_void_p),
         ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("block_ptrs", C.c_void_p), ("cu_blocks", C.c_void_p),
         ("layer_off", C.c_int64), ("rot_off", C.c_int64), ("dtype", C.c_int), ("stream", C.c_void_p),
     ]
@@ -54,6 +55,8 @@ def load():
     lib.b200h_gated_rms.argtypes = [P, P, P, L64, I, I, F, P, I, P]
     lib.b200h_route.argtypes = [P, P, I, I, I, I, P, P, P]
     lib.b200h_experts.argtypes = [P, P, P, P, P, P, I, I, I, I, P, I, P]
+    lib.b200h_silu_mul.argtypes = [P, P, P, L64, I, P]
+    lib.b200h_weighted_scatter.argtypes = [P, P, P, P, I, I, I, P]
     lib.b200h_argmax.argtypes = [P, L64, I, I, P, P]
     _lib = lib
     return lib

@@ -231,17 +231,21 @@ __global__ void latent_query_kernel(const T* __restrict__ q, int64_t ld_q, const
     for (int i = 2 * rot.pairs + threadIdx.x; i < rot_dim; i += blockDim.x) out[i] = to_f(qr[i]) * scale;
 }
 
-// Causal attention of one (row, head) per warp over the cached latents: score_j = q_lat . c_j + q_rot . kr_j, online softmax
-// that starts from the sink (a term exp(sink_h) in the denominator with no value), o_lat = sum_j w_j c_j.  Lane l owns the
-// latent coordinates l, l + 32, ...; a key's latent is loaded once and used for the score and for the weighted sum.
+// Causal attention of one (row, head, key range) per warp over the cached latents: score_j = q_lat . c_j + q_rot . kr_j, online
+// softmax, o_lat = sum_j w_j c_j.  Lane l owns the latent coordinates l, l + 32, ...; a key's latent is loaded once and used for
+// the score and for the weighted sum; four keys are in flight per iteration (independent dot products and reductions).
+// The keys of a row are cut into `splits` ranges of whole pages (blockIdx.z); range 0 starts its running maximum at the
+// sink (a term exp(sink_h) in the denominator with no value), the others empty.  Every range leaves an unnormalised partial
+// (max, denominator, weighted sum) that latent_out_kernel merges -- prompt portions run with one range, a step of single
+// decoded tokens with several, so that a few rows still fill the SMs.
 template <typename T, int NC, int NR>
 __global__ void latent_attention_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot, const float* __restrict__ sink,
                                         int heads, int kv_rank, int rot_dim, const int* __restrict__ tok_seq,
                                         const int* __restrict__ tok_pos, const int64_t* __restrict__ block_ptrs,
                                         const int* __restrict__ cu_blocks, int64_t layer_off, int block_len, int64_t rot_off,
-                                        float* __restrict__ o_lat)
+                                        int splits, float* __restrict__ o_lat, float* __restrict__ ml)
 {
-    const int t = blockIdx.x, h = blockIdx.y * blockDim.y + threadIdx.y, lane = threadIdx.x;
+    const int t = blockIdx.x, h = blockIdx.y * blockDim.y + threadIdx.y, z = blockIdx.z, lane = threadIdx.x;
     if (h >= heads) return;
     const int s = tok_seq[t], pos = tok_pos[t];
     float ql[NC], qr[NR], acc[NC];
@@ -251,14 +255,50 @@ __global__ void latent_attention_kernel(const float* __restrict__ q_lat, const f
     for (int i = 0; i < NC; ++i) { const int c = i * 32 + lane; ql[i] = c < kv_rank ? qlp[c] : 0.f; acc[i] = 0.f; }
 #pragma unroll
     for (int i = 0; i < NR; ++i) { const int c = i * 32 + lane; qr[i] = c < rot_dim ? qrp[c] : 0.f; }
-    float m = sink[h], l = 1.0f;
+    float m = z == 0 ? sink[h] : -1e30f, l = z == 0 ? 1.0f : 0.0f;
     const int64_t* pages = block_ptrs + cu_blocks[s];
-    for (int j0 = 0; j0 <= pos; j0 += block_len) {
-        const char* page = reinterpret_cast<const char*>(pages[j0 / block_len]) + layer_off;
+    const int n_pages = pos / block_len + 1, per = (n_pages + splits - 1) / splits;
+    const int p_lo = z * per, p_hi = min(n_pages, p_lo + per);
+    for (int pg = p_lo; pg < p_hi; ++pg) {
+        const char* page = reinterpret_cast<const char*>(pages[pg]) + layer_off;
         const T* cp = reinterpret_cast<const T*>(page);
         const float* rp = reinterpret_cast<const float*>(page + rot_off);
-        const int cnt = min(block_len, pos + 1 - j0);
-        for (int j = 0; j < cnt; ++j) {
+        const int cnt = min(block_len, pos + 1 - pg * block_len);
+        int j = 0;
+        for (; j + 4 <= cnt; j += 4) {
+            float cv[4][NC], part[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                part[u] = 0.f;
+#pragma unroll
+                for (int i = 0; i < NC; ++i) {
+                    const int c = i * 32 + lane;
+                    cv[u][i] = c < kv_rank ? to_f(cp[(size_t)(j + u) * kv_rank + c]) : 0.f;
+                    part[u] = fmaf(ql[i], cv[u][i], part[u]);
+                }
+#pragma unroll
+                for (int i = 0; i < NR; ++i) {
+                    const int c = i * 32 + lane;
+                    if (c < rot_dim) part[u] = fmaf(qr[i], rp[(size_t)(j + u) * rot_dim + c], part[u]);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) part[u] += __shfl_xor_sync(0xffffffffu, part[u], o);
+            }
+            const float mn = fmaxf(fmaxf(fmaxf(m, part[0]), fmaxf(part[1], part[2])), part[3]);
+            const float alpha = expf(m - mn);
+            float p[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) p[u] = expf(part[u] - mn);
+            l = l * alpha + ((p[0] + p[1]) + (p[2] + p[3]));
+#pragma unroll
+            for (int i = 0; i < NC; ++i)
+                acc[i] = acc[i] * alpha + ((p[0] * cv[0][i] + p[1] * cv[1][i]) + (p[2] * cv[2][i] + p[3] * cv[3][i]));
+            m = mn;
+        }
+        for (; j < cnt; ++j) {
             float cv[NC], part = 0.f;
 #pragma unroll
             for (int i = 0; i < NC; ++i) {
@@ -280,21 +320,32 @@ __global__ void latent_attention_kernel(const float* __restrict__ q_lat, const f
             m = mn;
         }
     }
-    const float inv = 1.0f / l;
-    float* out = o_lat + ((size_t)t * heads + h) * kv_rank;
+    const size_t at = ((size_t)t * heads + h) * splits + z;
+    float* out = o_lat + at * kv_rank;
 #pragma unroll
-    for (int i = 0; i < NC; ++i) { const int c = i * 32 + lane; if (c < kv_rank) out[c] = acc[i] * inv; }
+    for (int i = 0; i < NC; ++i) { const int c = i * 32 + lane; if (c < kv_rank) out[c] = acc[i]; }
+    if (lane == 0) { ml[2 * at] = m; ml[2 * at + 1] = l; }
 }
 
+// Merge of the key ranges' partials, value expansion and gate:
 // y[t, h*vdim + v] = (uv_h o_lat[t, h])[v] * sigmoid(gate[t, h*vdim + v]) as T.  One block per (row, head), a warp per value row.
 template <typename T>
-__global__ void latent_out_kernel(const float* __restrict__ o_lat, const T* __restrict__ uv, const T* __restrict__ gate, int64_t ld_gate,
-                                  int heads, int vdim, int kv_rank, T* __restrict__ y)
+__global__ void latent_out_kernel(const float* __restrict__ o_lat, const float* __restrict__ ml, int splits, const T* __restrict__ uv,
+                                  const T* __restrict__ gate, int64_t ld_gate, int heads, int vdim, int kv_rank, T* __restrict__ y)
 {
     extern __shared__ float sm[];
     const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const float* ol = o_lat + ((size_t)t * heads + h) * kv_rank;
-    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) sm[c] = ol[c];
+    const size_t at = ((size_t)t * heads + h) * splits;
+    float top = ml[2 * at];
+    for (int z = 1; z < splits; ++z) top = fmaxf(top, ml[2 * (at + z)]);
+    float den = 0.f;
+    for (int z = 0; z < splits; ++z) den += expf(ml[2 * (at + z)] - top) * ml[2 * (at + z) + 1];
+    const float inv = 1.0f / den;
+    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
+        float v = 0.f;
+        for (int z = 0; z < splits; ++z) v += expf(ml[2 * (at + z)] - top) * o_lat[(at + z) * kv_rank + c];
+        sm[c] = v * inv;
+    }
     __syncthreads();
     for (int v = warp; v < vdim; v += nw) {
         const T* row = uv + ((size_t)h * vdim + v) * kv_rank;
@@ -436,6 +487,26 @@ __global__ void expert_kernel(const T* __restrict__ x, const T* __restrict__ gat
         a = warp_sum(a);
         if (lane == 0) o[c] = wt * a;
     }
+}
+
+// The same experts for many rows (prompt portions): rows are grouped by expert on the host side of the step and every
+// expert runs three plain GEMMs over its rows; these two kernels are what lies between them.
+// mid = silu(g) * u, element by element, in float, stored as T.
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ g, const T* __restrict__ u, T* __restrict__ out, int64_t count)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = from_f<T>(silu_f(to_f(g[i])) * to_f(u[i]));
+}
+
+// out[slot[r]] = wts[slot[r]] * src[r]: row r of the expert-grouped result goes back to its (row, choice) place, weighted.
+template <typename T>
+__global__ void weighted_scatter_kernel(const T* __restrict__ src, const int* __restrict__ slot, const float* __restrict__ wts,
+                                        float* __restrict__ out, int width)
+{
+    const int r = blockIdx.x, to = slot[r];
+    const float wt = wts[to];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)to * width + i] = wt * to_f(src[(size_t)r * width + i]);
 }
 
 // ------------------------------------------------------------------------------------------------ arg-max of float rows
@@ -585,12 +656,12 @@ template <typename T>
 static int launch_latent_attention(const b200h_latent_args* a, cudaStream_t st)
 {
     const int hpb = a->heads < 4 ? a->heads : 4;
-    const dim3 grid(a->n, (a->heads + hpb - 1) / hpb), block(32, hpb);
+    const dim3 grid(a->n, (a->heads + hpb - 1) / hpb, a->splits), block(32, hpb);
     const int nc = (a->kv_rank + 31) / 32, nr = (a->rot_dim + 31) / 32;
 #define B200H_ATT(NC, NR)                                                                                                          \
     latent_attention_kernel<T, NC, NR><<<grid, block, 0, st>>>((const float*)a->q_lat, (const float*)a->q_rot, (const float*)a->sink, \
         a->heads, a->kv_rank, a->rot_dim, (const int*)a->tok_seq, (const int*)a->tok_pos, (const int64_t*)a->block_ptrs,            \
-        (const int*)a->cu_blocks, a->layer_off, a->block_len, a->rot_off, (float*)a->o_lat)
+        (const int*)a->cu_blocks, a->layer_off, a->block_len, a->rot_off, a->splits, (float*)a->o_lat, (float*)a->ml)
 #define B200H_ATT_R(NC)                                    \
     if (nr <= 1) B200H_ATT(NC, 1);                         \
     else if (nr <= 2) B200H_ATT(NC, 2);                    \
@@ -608,7 +679,7 @@ static int launch_latent_attention(const b200h_latent_args* a, cudaStream_t st)
 B200H_API int b200h_latent_attention(const b200h_latent_args* a)
 {
     if (!a || !a->q || !a->uk || !a->uv || !a->gate || !a->sink || !a->q_lat || !a->q_rot || !a->o_lat || !a->y || !a->block_ptrs ||
-        !a->tok_seq || !a->tok_pos || !a->cu_blocks)
+        !a->tok_seq || !a->tok_pos || !a->cu_blocks || !a->ml || a->splits < 1 || a->splits > 65535)
         return fail(B200H_ERR_INVALID_ARG, "latent_attention: bad arguments");
     if (a->kv_rank > 512 || a->rot_dim > 128) return fail(B200H_ERR_UNSUPPORTED, "latent_attention: kv_rank <= 512 and rot_dim <= 128");
     if (a->n == 0) return 0;
@@ -619,7 +690,8 @@ B200H_API int b200h_latent_attention(const b200h_latent_args* a)
         (const int*)a->tok_pos, (float*)a->q_lat, (float*)a->q_rot));
     B200H_DISPATCH_T(a->dtype, launch_latent_attention<T>(a, st));
     B200H_DISPATCH_T(a->dtype, latent_out_kernel<T><<<rows_heads, 128, a->kv_rank * sizeof(float), st>>>(
-        (const float*)a->o_lat, (const T*)a->uv, (const T*)a->gate, a->ld_gate, a->heads, a->vdim, a->kv_rank, (T*)a->y));
+        (const float*)a->o_lat, (const float*)a->ml, a->splits, (const T*)a->uv, (const T*)a->gate, a->ld_gate, a->heads, a->vdim, a->kv_rank,
+        (T*)a->y));
     return launched("latent_attention");
 }
 
@@ -677,6 +749,26 @@ B200H_API int b200h_experts(const void* x, const void* gate, const void* up, con
                                                          (const float*)wts, width, ff, top, (float*)out);
     });
     return launched("experts");
+}
+
+B200H_API int b200h_silu_mul(const void* g, const void* u, void* out, int64_t count, int dtype, void* stream)
+{
+    if (!g || !u || !out || count < 0) return fail(B200H_ERR_INVALID_ARG, "silu_mul: bad arguments");
+    if (count == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, silu_mul_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, st>>>((const T*)g, (const T*)u, (T*)out, count));
+    return launched("silu_mul");
+}
+
+B200H_API int b200h_weighted_scatter(const void* src, const void* slot, const void* wts, void* out, int rows, int width, int dtype,
+                                     void* stream)
+{
+    if (!src || !slot || !wts || !out || width <= 0) return fail(B200H_ERR_INVALID_ARG, "weighted_scatter: bad arguments");
+    if (rows == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, weighted_scatter_kernel<T><<<rows, 256, 0, st>>>((const T*)src, (const int*)slot, (const float*)wts, (float*)out,
+                                                                           width));
+    return launched("weighted_scatter");
 }
 
 B200H_API int b200h_argmax(const void* logits, int64_t ld, int rows, int vocab, void* out, void* stream)

@@ -261,7 +261,8 @@ class TurboMind:
         logits = self.model.step(n=n, batch=B, tokens=d_ctl[:n], tok_seq=d_ctl[n:2 * n], tok_pos=d_ctl[2 * n:3 * n],
                                  cu_q=d_ctl[o:o + B + 1], cu_blocks=d_ctl[o + B + 1:o + 2 * B + 2],
                                  seq_slot=d_ctl[o + 2 * B + 2:o + 3 * B + 2], block_ptrs=d_ptrs, state=self.state,
-                                 rows=d_ctl[o + 3 * B + 2:], n_rows=r, trace=getattr(self, "layer_trace", None))
+                                 rows=d_ctl[o + 3 * B + 2:], n_rows=r, max_pos=st["max_k_len"] - 1,
+                                 trace=getattr(self, "layer_trace", None))
         self.last_logits, self.last_rows = logits, {row: k for k, row in enumerate(uniq)}
         ids = self.model.argmax(logits).cpu().tolist()
         self.d2h_bytes += 4 * r

@@ -98,6 +98,8 @@ class HybridModel:
         self.slot_floats = slot
         self.w = {}
         self.weight_bytes = 0
+        self.grouped_experts_rows = 32    # steps of at least this many rows run the experts as grouped GEMMs
+        self.attention_warps = 148 * 16   # warps a latent-attention launch aims for (one per row, head and key range)
         self.events = None          # a list while profiling: (operator, start event, end event) of every timed region
         if spec.dtype == "f32":
             # float32 serving means true 32-bit products: no TF32, no reduced-precision accumulation
@@ -245,15 +247,16 @@ class HybridModel:
         return torch.mm(x, w.t())
 
     def step(self, *, n, batch, tokens, tok_seq, tok_pos, cu_q, seq_slot, block_ptrs, cu_blocks, state: StatePool, rows, n_rows,
-             trace=None):
+             max_pos, trace=None):
         """One mixed step.  Device tensors: tokens / tok_seq / tok_pos int32 [n]; cu_q, cu_blocks int32 [batch + 1]; seq_slot
-        int32 [batch]; block_ptrs int64 (page addresses); rows int32 [n_rows] = the rows whose logits are wanted.
+        int32 [batch]; block_ptrs int64 (page addresses); rows int32 [n_rows] = the rows whose logits are wanted; max_pos (host
+        int) = the largest position of the step.
         Returns float logits [n_rows, vocab].  trace: a list that receives a copy of the stream after every layer."""
         s, lib, w, dev, T, dt = self.spec, self.lib, self.w, self.device, self.T, self.dt
         W, eps, groups = s.width, s.norm_eps, s.norm_groups
         st = self._stream()
         c = StepArrays(n=n, batch=batch, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot, block_ptrs=block_ptrs,
-                       cu_blocks=cu_blocks, state=state)
+                       cu_blocks=cu_blocks, state=state, max_pos=max_pos)
         f32 = dict(dtype=torch.float32, device=dev)
         hist = torch.empty(len(s.layers) + 1, n, W, **f32)
         x = torch.empty(n, W, **f32)
@@ -336,7 +339,12 @@ class HybridModel:
             q = self._linear(cq, w[p + "uq"])
         q_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
         q_rot = torch.empty(n, m.heads, m.rot_dim, **f32)
-        o_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
+        # key ranges per row: one for prompt portions (rows x heads already fill the SMs), several whole-page ranges when a step
+        # of few rows would leave most SMs idle
+        splits = max(1, min(self.attention_warps // max(n * m.heads, 1), (c.max_pos // self.block_len + 1 + 1) // 2, 64))
+        o_lat = torch.empty(n, m.heads, splits, m.kv_rank, **f32)
+        ml = torch.empty(n, m.heads, splits, 2, **f32)
+        a.ml, a.splits = ml.data_ptr(), splits
         y = torch.empty(n, m.heads * m.vdim, dtype=T, device=dev)
         a.q, a.ld_q, a.uk, a.uv = q.data_ptr(), q.stride(0), w[p + "uk"].data_ptr(), w[p + "uv"].data_ptr()
         a.q_lat, a.q_rot, a.o_lat, a.y = q_lat.data_ptr(), q_rot.data_ptr(), o_lat.data_ptr(), y.data_ptr()
@@ -377,11 +385,40 @@ class HybridModel:
             H.check(lib.b200h_route(x.data_ptr(), w[p + "router"].data_ptr(), n, W, f.experts, f.top, ids.data_ptr(), wts.data_ptr(), st),
                     "route")
         out = torch.empty(n, f.top, W, dtype=torch.float32, device=dev)
+        self.last_routing = (ids, wts)
+        if n >= self.grouped_experts_rows and n * f.top >= 4 * f.experts:
+            with self.timed("experts (grouped GEMMs)"):
+                self._grouped_experts(i, xt, ids, wts, out, n)
+            return out
         with self.timed("experts"):
             H.check(lib.b200h_experts(xt.data_ptr(), w[p + "gate"].data_ptr(), w[p + "up"].data_ptr(), w[p + "down"].data_ptr(),
                                       ids.data_ptr(), wts.data_ptr(), n, W, f.ff, f.top, out.data_ptr(), self.dt, st), "experts")
-        self.last_routing = (ids, wts)
         return out
+
+    def _grouped_experts(self, i, xt, ids, wts, out, n):
+        """Prompt portions: rows are sorted by chosen expert (one host read of the per-expert counts), every expert runs its
+        gate / up / down GEMMs over its rows, and the results return to their (row, choice) places times the router's score.
+        A step of few rows uses the fused per-row kernel instead (b200h_experts), which reads an expert once per row."""
+        f, w, lib, st = self.spec.layers[i].mlp, self.w, self.lib, self._stream()
+        p = f"l{i}."
+        flat = ids.view(-1).long()
+        order = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=f.experts).cpu().tolist()
+        xg = xt.index_select(0, torch.div(order, f.top, rounding_mode="floor"))
+        m = n * f.top
+        res = torch.empty(m, self.spec.width, dtype=self.T, device=self.device)
+        at = 0
+        for e, cnt in enumerate(counts):
+            if cnt == 0:
+                continue
+            seg = xg[at:at + cnt]
+            g, u = torch.mm(seg, w[p + "gate"][e].t()), torch.mm(seg, w[p + "up"][e].t())
+            H.check(lib.b200h_silu_mul(g.data_ptr(), u.data_ptr(), g.data_ptr(), g.numel(), self.dt, st), "silu_mul")
+            torch.mm(g, w[p + "down"][e].t(), out=res[at:at + cnt])
+            at += cnt
+        slot = order.to(torch.int32)
+        H.check(lib.b200h_weighted_scatter(res.data_ptr(), slot.data_ptr(), wts.data_ptr(), out.data_ptr(), m, self.spec.width, self.dt, st),
+                "weighted_scatter")
 
     def argmax(self, logits):
         """Greedy ids of float logits [r, vocab] (device int32 [r])."""

@@ -187,6 +187,16 @@ class EmulatedHybridLib:
                 O[t, k] = wt[t, k] * (Dn[e] @ (g * _sigmoid(g) * (U[e] @ X[t])))
         return 0
 
+    def b200h_silu_mul(self, g, u, out, count, dtype, stream):
+        G_, U_ = _a(g, count).copy(), _a(u, count).copy()
+        _a(out, count)[:] = G_ * _sigmoid(G_) * U_
+        return 0
+
+    def b200h_weighted_scatter(self, src, slot, wts, out, rows, width, dtype, stream):
+        S_, to, wt = _f(src, rows, width), _i(slot, rows), _a(wts, rows)
+        _f(out, rows, width)[to] = wt[to][:, None] * S_
+        return 0
+
     def b200h_argmax(self, logits, ld, rows, vocab, out, stream):
         _i(out, rows)[:] = _rows(logits, rows, ld, vocab).argmax(-1)
         return 0

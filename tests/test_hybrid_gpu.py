@@ -43,7 +43,7 @@ def _ctx(eng, start, n, pages, slot=2):
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
     ptrs = torch.tensor([eng.pool.base + b * eng.pool.block_bytes for b in pages], dtype=torch.int64, device=dev)
     return StepArrays(n=n, batch=1, tok_seq=i32([0] * n), tok_pos=i32(list(range(start, start + n))), cu_q=i32([0, n]), seq_slot=i32([slot]),
-                      block_ptrs=ptrs, cu_blocks=i32([0, len(pages)]), state=eng.state)
+                      block_ptrs=ptrs, cu_blocks=i32([0, len(pages)]), state=eng.state, max_pos=start + n - 1)
 
 
 def _bf(t):
