@@ -107,10 +107,23 @@ B200H_API int b200h_gated_rms(const void* o, const void* w, const void* gate, in
 /* softmax(router x) over all experts; ids / wts [n, top]: the top largest and their scores. */
 B200H_API int b200h_route(const void* x, const void* router, int n, int width, int experts, int top, void* ids, void* wts, void* stream);
 
-/* out[t, k] = wts[t, k] * down_e (silu(gate_e x[t]) * (up_e x[t])), e = ids[t, k]; gate, up T [experts, ff, width], down T [experts, width, ff];
- * out float [n, top, width]. */
-B200H_API int b200h_experts(const void* x, const void* gate, const void* up, const void* down, const void* ids, const void* wts, int n,
-                            int width, int ff, int top, void* out, int dtype, void* stream);
+/* Routed experts for a step of few rows (an expert's weights are read once for all rows that chose it):
+ * out[t, k] = wts[t, k] * down_e (silu(gate_e x[t]) * (up_e x[t])), e = ids[t, k]. */
+typedef struct b200h_expert_args {
+    int n, width, ff, experts, top, dtype;
+    const void* x;           /* T [n, width] */
+    const void* gate;        /* T [experts, ff, width] */
+    const void* up;          /* T [experts, ff, width] */
+    const void* down;        /* T [experts, width, ff] */
+    const void* ids;         /* int [n, top] */
+    const void* wts;         /* float [n, top] */
+    void* out;               /* float [n, top, width] */
+    void* mid;               /* T [n * top, ff] scratch */
+    void* counts;            /* int [experts] scratch */
+    void* lists;             /* int [experts, n * top] scratch */
+    void* stream;
+} b200h_expert_args;
+B200H_API int b200h_experts(const b200h_expert_args* args);
 
 /* out = silu(g) * u element by element (T, `count` elements): between an expert's gate / up GEMMs and its down GEMM. */
 B200H_API int b200h_silu_mul(const void* g, const void* u, void* out, int64_t count, int dtype, void* stream);

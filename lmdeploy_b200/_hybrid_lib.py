@@ -29,6 +29,15 @@ class LatentArgs(C.Structure):
     ]
 
 
+class ExpertArgs(C.Structure):
+    """b200h_expert_args."""
+    _fields_ = [
+        ("n", C.c_int), ("width", C.c_int), ("ff", C.c_int), ("experts", C.c_int), ("top", C.c_int), ("dtype", C.c_int),
+        ("x", C.c_void_p), ("gate", C.c_void_p), ("up", C.c_void_p), ("down", C.c_void_p), ("ids", C.c_void_p), ("wts", C.c_void_p),
+        ("out", C.c_void_p), ("mid", C.c_void_p), ("counts", C.c_void_p), ("lists", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
 _lib = None
 P, I, L64, F = C.c_void_p, C.c_int, C.c_int64, C.c_float
 
@@ -54,7 +63,7 @@ def load():
     lib.b200h_decay_attention.argtypes = [P, P, P, L64, P, P, L64, P, P, I, I, I, I, P, I, P]
     lib.b200h_gated_rms.argtypes = [P, P, P, L64, I, I, F, P, I, P]
     lib.b200h_route.argtypes = [P, P, I, I, I, I, P, P, P]
-    lib.b200h_experts.argtypes = [P, P, P, P, P, P, I, I, I, I, P, I, P]
+    lib.b200h_experts.argtypes = [C.POINTER(ExpertArgs)]
     lib.b200h_silu_mul.argtypes = [P, P, P, L64, I, P]
     lib.b200h_weighted_scatter.argtypes = [P, P, P, P, I, I, I, P]
     lib.b200h_argmax.argtypes = [P, L64, I, I, P, P]

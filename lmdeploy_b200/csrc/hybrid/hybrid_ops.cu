@@ -451,41 +451,124 @@ __global__ void route_kernel(const float* __restrict__ x, const float* __restric
     }
 }
 
-// One block per (row, chosen expert): mid = silu(gate_e x) * (up_e x), out[t, k] = weight * down_e mid.  Expert weights are
-// stacked: gate, up [experts, ff, width], down [experts, width, ff].  The k partial results are summed by the norm that follows.
-template <typename T>
-__global__ void expert_kernel(const T* __restrict__ x, const T* __restrict__ gate, const T* __restrict__ up, const T* __restrict__ down,
-                              const int* __restrict__ ids, const float* __restrict__ wts, int width, int ff, int top,
-                              float* __restrict__ out)
+// Experts for a step of few rows, expert-major so that an expert's weights stream from HBM once whatever the number of rows
+// that chose it.  Entry i = (row i / top, choice i % top).  expert_lists_kernel collects every expert's entries;
+// expert_rows_kernel gives a block 32 weight rows of one expert and walks that expert's entries eight at a time: the
+// eight input rows sit in shared memory as T, a warp takes one weight row at a time, every lane reads its 16-byte pieces of
+// the row once and feeds eight float accumulators, and the warp reduces them.
+//   DUAL: out[i, r] = silu(gate_e[r] . x) * (up_e[r] . x) as T        (x = the row's stream as T, K = width, R = ff)
+//   else: out[i, r] = wts[i] * (down_e[r] . mid[i]) as float           (K = ff, R = width)
+// The order of an expert's list depends on the atomics' order; every entry's result lands in its own place, so the numbers do not.
+__global__ void expert_lists_kernel(const int* __restrict__ ids, int entries, int experts, int* __restrict__ counts, int* __restrict__ lists)
 {
-    extern __shared__ float sm[];
-    float* xs = sm;
-    float* mid = sm + width;
-    const int t = blockIdx.x, k = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const int e = ids[(size_t)t * top + k];
-    const float wt = wts[(size_t)t * top + k];
-    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(x[(size_t)t * width + i]);
+    extern __shared__ int cnt[];
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
     __syncthreads();
-    const T* ge = gate + (size_t)e * ff * width;
-    const T* ue = up + (size_t)e * ff * width;
-    for (int f = warp; f < ff; f += nw) {
-        float a = 0.f, b = 0.f;
-        for (int i = lane; i < width; i += 32) {
-            a = fmaf(to_f(ge[(size_t)f * width + i]), xs[i], a);
-            b = fmaf(to_f(ue[(size_t)f * width + i]), xs[i], b);
-        }
-        a = warp_sum(a);
-        b = warp_sum(b);
-        if (lane == 0) mid[f] = silu_f(a) * b;
+    for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+        const int e = ids[i];
+        lists[(size_t)e * entries + atomicAdd(&cnt[e], 1)] = i;
     }
     __syncthreads();
-    const T* de = down + (size_t)e * width * ff;
-    float* o = out + ((size_t)t * top + k) * width;
-    for (int c = warp; c < width; c += nw) {
-        float a = 0.f;
-        for (int i = lane; i < ff; i += 32) a = fmaf(to_f(de[(size_t)c * ff + i]), mid[i], a);
-        a = warp_sum(a);
-        if (lane == 0) o[c] = wt * a;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = cnt[e];
+}
+
+constexpr int kExpertTile = 8;         // entries per pass over an expert's weight rows
+constexpr int kExpertRows = 32;        // weight rows per block
+
+template <typename T> struct Pack;     // 16 bytes of T
+template <> struct Pack<bf16> { static constexpr int N = 8; };
+template <> struct Pack<float> { static constexpr int N = 4; };
+
+template <typename T>
+__device__ __forceinline__ void load_pack(const T* p, float (&v)[Pack<T>::N]);
+template <>
+__device__ __forceinline__ void load_pack<bf16>(const bf16* p, float (&v)[8])
+{
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+template <>
+__device__ __forceinline__ void load_pack<float>(const float* p, float (&v)[4])
+{
+    const float4 raw = *reinterpret_cast<const float4*>(p);
+    v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+}
+
+template <typename T, bool DUAL, bool VEC>
+__global__ void expert_rows_kernel(const T* __restrict__ x, int x_div, const T* __restrict__ wa, const T* __restrict__ wb,
+                                   const int* __restrict__ counts, const int* __restrict__ lists, int entries,
+                                   const float* __restrict__ wts, int K, int R, void* __restrict__ out_)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* xs = reinterpret_cast<T*>(smem_raw);                     // [kExpertTile][K]
+    const int e = blockIdx.y, r0 = blockIdx.x * kExpertRows;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int count = counts[e];
+    const int* list = lists + (size_t)e * entries;
+    const T* wae = wa + (size_t)e * R * K;
+    const T* wbe = DUAL ? wb + (size_t)e * R * K : nullptr;
+    constexpr int P = Pack<T>::N;
+    for (int base = 0; base < count; base += kExpertTile) {
+        const int live = min(kExpertTile, count - base);
+        __syncthreads();
+        for (int u = 0; u < kExpertTile; ++u) {
+            const T* src = u < live ? x + (size_t)(list[base + u] / x_div) * K : nullptr;
+            for (int i = threadIdx.x; i < K; i += blockDim.x) xs[(size_t)u * K + i] = src ? src[i] : from_f<T>(0.f);
+        }
+        __syncthreads();
+        for (int r = r0 + warp; r < min(R, r0 + kExpertRows); r += nw) {
+            float a[kExpertTile], b[kExpertTile];
+#pragma unroll
+            for (int u = 0; u < kExpertTile; ++u) a[u] = b[u] = 0.f;
+            const T* ra = wae + (size_t)r * K;
+            const T* rb = DUAL ? wbe + (size_t)r * K : nullptr;
+            if (VEC) {
+                for (int i = lane * P; i < K; i += 32 * P) {
+                    float va[P], vb[P];
+                    load_pack<T>(ra + i, va);
+                    if (DUAL) load_pack<T>(rb + i, vb);
+#pragma unroll
+                    for (int u = 0; u < kExpertTile; ++u) {
+                        float xv[P];
+                        load_pack<T>(xs + (size_t)u * K + i, xv);
+#pragma unroll
+                        for (int k = 0; k < P; ++k) {
+                            a[u] = fmaf(va[k], xv[k], a[u]);
+                            if (DUAL) b[u] = fmaf(vb[k], xv[k], b[u]);
+                        }
+                    }
+                }
+            } else {
+                for (int i = lane; i < K; i += 32) {
+                    const float va = to_f(ra[i]), vb = DUAL ? to_f(rb[i]) : 0.f;
+#pragma unroll
+                    for (int u = 0; u < kExpertTile; ++u) {
+                        const float xv = to_f(xs[(size_t)u * K + i]);
+                        a[u] = fmaf(va, xv, a[u]);
+                        if (DUAL) b[u] = fmaf(vb, xv, b[u]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kExpertTile; ++u) {
+                a[u] = warp_sum(a[u]);
+                if (DUAL) b[u] = warp_sum(b[u]);
+            }
+            if (lane < live) {
+                float va = 0.f, vb = 0.f;
+#pragma unroll
+                for (int u = 0; u < kExpertTile; ++u)
+                    if (u == lane) { va = a[u]; vb = b[u]; }
+                const int entry = list[base + lane];
+                if (DUAL) reinterpret_cast<T*>(out_)[(size_t)entry * R + r] = from_f<T>(silu_f(va) * vb);
+                else reinterpret_cast<float*>(out_)[(size_t)entry * R + r] = wts[entry] * va;
+            }
+        }
     }
 }
 
@@ -735,19 +818,43 @@ B200H_API int b200h_route(const void* x, const void* router, int n, int width, i
     return launched("route");
 }
 
-B200H_API int b200h_experts(const void* x, const void* gate, const void* up, const void* down, const void* ids, const void* wts, int n,
-                            int width, int ff, int top, void* out, int dtype, void* stream)
+template <typename T>
+static void launch_expert_rows(const b200h_expert_args* a, cudaStream_t st)
 {
-    if (!x || !gate || !up || !down || !ids || !wts || !out || ff <= 0) return fail(B200H_ERR_INVALID_ARG, "experts: bad arguments");
-    if (n == 0) return 0;
-    const size_t smem = (size_t)(width + ff) * sizeof(float);
-    if (smem > 200 * 1024) return fail(B200H_ERR_UNSUPPORTED, "experts: width + ff exceeds shared memory");
-    cudaStream_t st = (cudaStream_t)stream;
-    B200H_DISPATCH_T(dtype, {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(expert_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        expert_kernel<T><<<dim3(n, top), 256, smem, st>>>((const T*)x, (const T*)gate, (const T*)up, (const T*)down, (const int*)ids,
-                                                         (const float*)wts, width, ff, top, (float*)out);
-    });
+    const int entries = a->n * a->top;
+    const bool vec = a->width % Pack<T>::N == 0 && a->ff % Pack<T>::N == 0;
+    const size_t sm_up = (size_t)kExpertTile * a->width * sizeof(T), sm_down = (size_t)kExpertTile * a->ff * sizeof(T);
+    const dim3 g_up((a->ff + kExpertRows - 1) / kExpertRows, a->experts), g_down((a->width + kExpertRows - 1) / kExpertRows, a->experts);
+#define B200H_ROWS(DUAL, VEC, GRID, SM, X, DIV, WA, WB, K, R, OUT)                                                                      \
+    do {                                                                                                                               \
+        if ((SM) > 48 * 1024)                                                                                                          \
+            cudaFuncSetAttribute(expert_rows_kernel<T, DUAL, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SM));            \
+        expert_rows_kernel<T, DUAL, VEC><<<GRID, 256, SM, st>>>((const T*)(X), DIV, (const T*)(WA), (const T*)(WB), (const int*)a->counts, \
+                                                               (const int*)a->lists, entries, (const float*)a->wts, K, R, OUT);         \
+    } while (0)
+    if (vec) {
+        B200H_ROWS(true, true, g_up, sm_up, a->x, a->top, a->gate, a->up, a->width, a->ff, a->mid);
+        B200H_ROWS(false, true, g_down, sm_down, a->mid, 1, a->down, nullptr, a->ff, a->width, a->out);
+    } else {
+        B200H_ROWS(true, false, g_up, sm_up, a->x, a->top, a->gate, a->up, a->width, a->ff, a->mid);
+        B200H_ROWS(false, false, g_down, sm_down, a->mid, 1, a->down, nullptr, a->ff, a->width, a->out);
+    }
+#undef B200H_ROWS
+}
+
+B200H_API int b200h_experts(const b200h_expert_args* a)
+{
+    if (!a || !a->x || !a->gate || !a->up || !a->down || !a->ids || !a->wts || !a->out || !a->mid || !a->counts || !a->lists ||
+        a->ff <= 0 || a->experts <= 0 || a->top <= 0)
+        return fail(B200H_ERR_INVALID_ARG, "experts: bad arguments");
+    if (a->n == 0) return 0;
+    const size_t widest = (size_t)kExpertTile * (a->width > a->ff ? a->width : a->ff) * (a->dtype == B200H_F32 ? 4 : 2);
+    if (widest > 200 * 1024) return fail(B200H_ERR_UNSUPPORTED, "experts: eight rows of width / ff exceed shared memory");
+    if ((size_t)a->experts * sizeof(int) > 48 * 1024) return fail(B200H_ERR_UNSUPPORTED, "experts: more than 12288 experts");
+    cudaStream_t st = (cudaStream_t)a->stream;
+    expert_lists_kernel<<<1, 1024, a->experts * sizeof(int), st>>>((const int*)a->ids, a->n * a->top, a->experts, (int*)a->counts,
+                                                                  (int*)a->lists);
+    B200H_DISPATCH_T(a->dtype, launch_expert_rows<T>(a, st));
     return launched("experts");
 }
 

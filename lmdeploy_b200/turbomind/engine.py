@@ -156,6 +156,9 @@ class TurboMind:
                                    prefill_chunk=max(1, cfg.max_prefill_token_num), token_budget=budget, state_slots=self.max_batch)
         self.last_logits = None          # float logits [rows, vocab] of the last step and the row each belongs to
         self.last_rows = {}
+        self._max_blocks = (self.session_len + self.block_len - 1) // self.block_len
+        self._use_graphs = os.environ.get("B200_ENGINE_GRAPHS", "1") != "0"
+        self._hybrid_graphs, self._hybrid_seen = {}, set()
 
     @classmethod
     def from_pretrained(cls, pretrained_model_name_or_path, engine_config=None, **kw):
@@ -255,14 +258,45 @@ class TurboMind:
         pin = dev.type == "cuda"
         h_ctl = torch.from_numpy(ctl)
         h_ptrs = torch.from_numpy(ptrs)
-        d_ctl = (h_ctl.pin_memory() if pin else h_ctl).to(dev, non_blocking=True)
-        d_ptrs = (h_ptrs.pin_memory() if pin else h_ptrs).to(dev, non_blocking=True)
+        if pin:
+            h_ctl, h_ptrs = h_ctl.pin_memory(), h_ptrs.pin_memory()
         self.h2d_bytes += ctl.nbytes + ptrs.nbytes
-        logits = self.model.step(n=n, batch=B, tokens=d_ctl[:n], tok_seq=d_ctl[n:2 * n], tok_pos=d_ctl[2 * n:3 * n],
-                                 cu_q=d_ctl[o:o + B + 1], cu_blocks=d_ctl[o + B + 1:o + 2 * B + 2],
-                                 seq_slot=d_ctl[o + 2 * B + 2:o + 3 * B + 2], block_ptrs=d_ptrs, state=self.state,
-                                 rows=d_ctl[o + 3 * B + 2:], n_rows=r, max_pos=st["max_k_len"] - 1,
-                                 trace=getattr(self, "layer_trace", None))
+        max_pos = st["max_k_len"] - 1
+        trace = getattr(self, "layer_trace", None)
+
+        def run(d_ctl, d_ptrs):
+            return self.model.step(n=n, batch=B, tokens=d_ctl[:n], tok_seq=d_ctl[n:2 * n], tok_pos=d_ctl[2 * n:3 * n],
+                                   cu_q=d_ctl[o:o + B + 1], cu_blocks=d_ctl[o + B + 1:o + 2 * B + 2],
+                                   seq_slot=d_ctl[o + 2 * B + 2:o + 3 * B + 2], block_ptrs=d_ptrs, state=self.state,
+                                   rows=d_ctl[o + 3 * B + 2:], n_rows=r, max_pos=max_pos, trace=trace)
+
+        # A step of single decoded tokens is shape-static given its batch size and the attention's key ranges: every array lives
+        # in a fixed device buffer, so its launches are replayed from a CUDA graph, captured the second time the key is seen
+        # (the engine does the same for dense models, per batch size).
+        key = (B, self.model.decode_key(n, max_pos)) if n == B and uniq == list(range(B)) else None
+        if key is not None and self._use_graphs and pin and trace is None and self.model.events is None:
+            g = self._hybrid_graphs.get(key)
+            if g is None and key in self._hybrid_seen:
+                g = dict(ctl=torch.zeros(len(ctl), dtype=torch.int32, device=dev),
+                         ptrs=torch.zeros(B * self._max_blocks, dtype=torch.int64, device=dev))
+                g["ctl"].copy_(h_ctl)
+                torch.cuda.synchronize(dev)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    g["logits"] = run(g["ctl"], g["ptrs"])
+                    g["ids"] = self.model.argmax(g["logits"])
+                g["graph"] = graph
+                self._hybrid_graphs[key] = g
+            self._hybrid_seen.add(key)
+            if g is not None:
+                g["ctl"].copy_(h_ctl, non_blocking=True)
+                g["ptrs"][:len(ptrs)].copy_(h_ptrs, non_blocking=True)
+                g["graph"].replay()
+                self.last_logits, self.last_rows = g["logits"], {row: k for k, row in enumerate(uniq)}
+                ids = g["ids"].cpu().tolist()
+                self.d2h_bytes += 4 * r
+                return {row: ids[k] for k, row in enumerate(uniq)}
+        logits = run(h_ctl.to(dev, non_blocking=True), h_ptrs.to(dev, non_blocking=True))
         self.last_logits, self.last_rows = logits, {row: k for k, row in enumerate(uniq)}
         ids = self.model.argmax(logits).cpu().tolist()
         self.d2h_bytes += 4 * r

@@ -98,7 +98,7 @@ class HybridModel:
         self.slot_floats = slot
         self.w = {}
         self.weight_bytes = 0
-        self.grouped_experts_rows = 32    # steps of at least this many rows run the experts as grouped GEMMs
+        self.grouped_experts_rows = 24    # steps that give an expert this many rows on average run the experts as grouped GEMMs
         self.attention_warps = 148 * 16   # warps a latent-attention launch aims for (one per row, head and key range)
         self.events = None          # a list while profiling: (operator, start event, end event) of every timed region
         if spec.dtype == "f32":
@@ -300,6 +300,19 @@ class HybridModel:
             return torch.mm(xn.float(), head.float().t())
 
     # ---- the mechanisms, one method each (the step above strings them together; tests call them alone)
+    def attention_splits(self, n, heads, max_pos):
+        """Key ranges per row of a latent-attention launch: enough to reach `attention_warps` warps, at least two pages each,
+        a power of two (so that a growing context changes it rarely: the engine keys its decode graphs on it)."""
+        want = min(self.attention_warps // max(n * heads, 1), (max_pos // self.block_len + 2) // 2, 64)
+        splits = 1
+        while splits * 2 <= want:
+            splits *= 2
+        return splits
+
+    def decode_key(self, n, max_pos):
+        """What a captured decode step depends on besides its row count."""
+        return tuple(self.attention_splits(n, l.mixer.heads, max_pos) for l in self.spec.layers if l.mixer.kind == "latent_attention")
+
     def conv_input(self, i, x, c):
         """What layer i's mixer reads: x + causal convolution of x over the sequence (as T); advances the layer's conv state."""
         s, w = self.spec, self.w
@@ -341,7 +354,7 @@ class HybridModel:
         q_rot = torch.empty(n, m.heads, m.rot_dim, **f32)
         # key ranges per row: one for prompt portions (rows x heads already fill the SMs), several whole-page ranges when a step
         # of few rows would leave most SMs idle
-        splits = max(1, min(self.attention_warps // max(n * m.heads, 1), (c.max_pos // self.block_len + 1 + 1) // 2, 64))
+        splits = self.attention_splits(n, m.heads, c.max_pos)
         o_lat = torch.empty(n, m.heads, splits, m.kv_rank, **f32)
         ml = torch.empty(n, m.heads, splits, 2, **f32)
         a.ml, a.splits = ml.data_ptr(), splits
@@ -386,19 +399,25 @@ class HybridModel:
                     "route")
         out = torch.empty(n, f.top, W, dtype=torch.float32, device=dev)
         self.last_routing = (ids, wts)
-        if n >= self.grouped_experts_rows and n * f.top >= 4 * f.experts:
+        if n * f.top >= self.grouped_experts_rows * f.experts:
             with self.timed("experts (grouped GEMMs)"):
                 self._grouped_experts(i, xt, ids, wts, out, n)
             return out
         with self.timed("experts"):
-            H.check(lib.b200h_experts(xt.data_ptr(), w[p + "gate"].data_ptr(), w[p + "up"].data_ptr(), w[p + "down"].data_ptr(),
-                                      ids.data_ptr(), wts.data_ptr(), n, W, f.ff, f.top, out.data_ptr(), self.dt, st), "experts")
+            a = H.ExpertArgs()
+            a.n, a.width, a.ff, a.experts, a.top, a.dtype = n, W, f.ff, f.experts, f.top, self.dt
+            a.x, a.gate, a.up, a.down = xt.data_ptr(), w[p + "gate"].data_ptr(), w[p + "up"].data_ptr(), w[p + "down"].data_ptr()
+            a.ids, a.wts, a.out = ids.data_ptr(), wts.data_ptr(), out.data_ptr()
+            mid = torch.empty(n * f.top, f.ff, dtype=self.T, device=dev)
+            lists = torch.empty(f.experts * (n * f.top + 1), dtype=torch.int32, device=dev)
+            a.mid, a.counts, a.lists, a.stream = mid.data_ptr(), lists.data_ptr(), lists.data_ptr() + 4 * f.experts, st
+            H.check(lib.b200h_experts(C.byref(a)), "experts")
         return out
 
     def _grouped_experts(self, i, xt, ids, wts, out, n):
         """Prompt portions: rows are sorted by chosen expert (one host read of the per-expert counts), every expert runs its
         gate / up / down GEMMs over its rows, and the results return to their (row, choice) places times the router's score.
-        A step of few rows uses the fused per-row kernel instead (b200h_experts), which reads an expert once per row."""
+        A step of few rows uses the expert-major kernels instead (b200h_experts: no host read, every expert's weights once)."""
         f, w, lib, st = self.spec.layers[i].mlp, self.w, self.lib, self._stream()
         p = f"l{i}."
         flat = ids.view(-1).long()

@@ -175,11 +175,12 @@ class EmulatedHybridLib:
         _f(wts, n, top)[:] = np.take_along_axis(sc, order, -1)
         return 0
 
-    def b200h_experts(self, x, gate, up, down, ids, wts, n, width, ff, top, out, dtype, stream):
-        X, idx, wt = _f(x, n, width), _i(ids, n * top).reshape(n, top), _f(wts, n, top)
-        E = int(idx.max()) + 1
-        G, U, Dn = _f(gate, E, ff, width), _f(up, E, ff, width), _f(down, E, width, ff)
-        O = _f(out, n, top, width)
+    def b200h_experts(self, args):
+        a = args._obj
+        n, top, width, ff, E = a.n, a.top, a.width, a.ff, a.experts
+        X, idx, wt = _f(a.x, n, width), _i(a.ids, n * top).reshape(n, top), _f(a.wts, n, top)
+        G, U, Dn = _f(a.gate, E, ff, width), _f(a.up, E, ff, width), _f(a.down, E, width, ff)
+        O = _f(a.out, n, top, width)
         for t in range(n):
             for k in range(top):
                 e = idx[t, k]

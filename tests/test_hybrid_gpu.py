@@ -203,3 +203,20 @@ def test_do_sample_through_the_engine_is_a_function_of_the_seed():
          GenerationConfig(max_new_tokens=12, ignore_eos=True)])]
     a, b, c = run(1), run(1), run(2)
     assert a == b and a[0] != c[0] and a[1] == c[1]
+
+
+def test_decode_graph_replay_equals_eager_launches(monkeypatch):
+    """Steps of single decoded tokens replay from a CUDA graph per (batch size, key ranges); the tokens are those of eager launches."""
+    from lmdeploy_b200.messages import GenerationConfig
+    from lmdeploy_b200.turbomind.engine import batched_generate
+    cfg = HC.config()
+    w = HC.random_tensors(cfg, seed=11)
+    P = HC.prompts_for(cfg, {"a": 9, "b": 70, "c": 3})
+    out = {}
+    for graphs in ("0", "1"):
+        monkeypatch.setenv("B200_ENGINE_GRAPHS", graphs)
+        eng = HC.build_engine(cfg, w, device="cuda", dtype="f32")
+        seqs = batched_generate(eng, [P[k] for k in "abc"], GenerationConfig(max_new_tokens=80, ignore_eos=True))
+        out[graphs] = [list(s.generated) for s in seqs]
+        assert bool(eng._hybrid_graphs) == (graphs == "1")
+    assert out["0"] == out["1"]
