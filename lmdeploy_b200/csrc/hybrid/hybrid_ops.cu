@@ -233,20 +233,43 @@ __global__ void latent_query_kernel(const T* __restrict__ q, int64_t ld_q, const
 
 // Causal attention of one (row, head, key range) per warp over the cached latents: score_j = q_lat . c_j + q_rot . kr_j, online
 // softmax, o_lat = sum_j w_j c_j.  Lane l owns the latent coordinates l, l + 32, ...; a key's latent is loaded once and used for
-// the score and for the weighted sum; four keys are in flight per iteration (independent dot products and reductions).
+// the score and for the weighted sum; four keys are in flight per iteration (independent dot products and reductions).  The
+// warps of a block are heads of the same row: sixteen keys at a time are staged in shared memory once for all of them.
 // The keys of a row are cut into `splits` ranges of whole pages (blockIdx.z); range 0 starts its running maximum at the
 // sink (a term exp(sink_h) in the denominator with no value), the others empty.  Every range leaves an unnormalised partial
 // (max, denominator, weighted sum) that latent_out_kernel merges -- prompt portions run with one range, a step of single
 // decoded tokens with several, so that a few rows still fill the SMs.
+constexpr int kKeyTile = 16;           // keys staged in shared memory at a time, shared by the heads of the block
+
+// Copy `bytes` (a multiple of `unit`) from global to shared memory with the whole block: 16-byte pieces when both allow it.
+__device__ __forceinline__ void stage(void* dst, const void* src, int bytes, int unit, int tid, int nthreads)
+{
+    if (unit % 16 == 0) {
+        for (int i = tid; i < bytes / 16; i += nthreads) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else if (unit % 4 == 0) {
+        for (int i = tid; i < bytes / 4; i += nthreads) reinterpret_cast<unsigned*>(dst)[i] = reinterpret_cast<const unsigned*>(src)[i];
+    } else {
+        for (int i = tid; i < bytes / 2; i += nthreads)
+            reinterpret_cast<unsigned short*>(dst)[i] = reinterpret_cast<const unsigned short*>(src)[i];
+    }
+}
+
 template <typename T, int NC, int NR>
-__global__ void latent_attention_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot, const float* __restrict__ sink,
+__global__ void __launch_bounds__(256, 2) latent_attention_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot, const float* __restrict__ sink,
                                         int heads, int kv_rank, int rot_dim, const int* __restrict__ tok_seq,
                                         const int* __restrict__ tok_pos, const int64_t* __restrict__ block_ptrs,
                                         const int* __restrict__ cu_blocks, int64_t layer_off, int block_len, int64_t rot_off,
                                         int splits, float* __restrict__ o_lat, float* __restrict__ ml)
 {
-    const int t = blockIdx.x, h = blockIdx.y * blockDim.y + threadIdx.y, z = blockIdx.z, lane = threadIdx.x;
-    if (h >= heads) return;
+    extern __shared__ __align__(16) unsigned char tile_raw[];
+    const int c_row = kv_rank * (int)sizeof(T), r_row = rot_dim * (int)sizeof(float);
+    T* cs = reinterpret_cast<T*>(tile_raw);                                                       // [kKeyTile][kv_rank]
+    float* rs = reinterpret_cast<float*>(tile_raw + (kKeyTile * c_row + 15) / 16 * 16);           // [kKeyTile][rot_dim]
+    const int t = blockIdx.x, z = blockIdx.z, lane = threadIdx.x;
+    const int tid = threadIdx.y * 32 + lane, nthreads = blockDim.y * 32;
+    const int h_raw = blockIdx.y * blockDim.y + threadIdx.y;
+    const bool live = h_raw < heads;                  // a warp past the last head still helps staging and meets the barriers
+    const int h = live ? h_raw : heads - 1;
     const int s = tok_seq[t], pos = tok_pos[t];
     float ql[NC], qr[NR], acc[NC];
     const float* qlp = q_lat + ((size_t)t * heads + h) * kv_rank;
@@ -261,65 +284,72 @@ __global__ void latent_attention_kernel(const float* __restrict__ q_lat, const f
     const int p_lo = z * per, p_hi = min(n_pages, p_lo + per);
     for (int pg = p_lo; pg < p_hi; ++pg) {
         const char* page = reinterpret_cast<const char*>(pages[pg]) + layer_off;
-        const T* cp = reinterpret_cast<const T*>(page);
-        const float* rp = reinterpret_cast<const float*>(page + rot_off);
         const int cnt = min(block_len, pos + 1 - pg * block_len);
-        int j = 0;
-        for (; j + 4 <= cnt; j += 4) {
-            float cv[4][NC], part[4];
+        for (int j0 = 0; j0 < cnt; j0 += kKeyTile) {
+            const int kt = min(kKeyTile, cnt - j0);
+            __syncthreads();
+            stage(cs, page + (size_t)j0 * c_row, kt * c_row, c_row, tid, nthreads);
+            stage(rs, page + rot_off + (size_t)j0 * r_row, kt * r_row, r_row, tid, nthreads);
+            __syncthreads();
+            if (!live) continue;
+            int j = 0;
+            for (; j + 4 <= kt; j += 4) {
+                float cv[4][NC], part[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                part[u] = 0.f;
+                for (int u = 0; u < 4; ++u) {
+                    part[u] = 0.f;
+#pragma unroll
+                    for (int i = 0; i < NC; ++i) {
+                        const int c = i * 32 + lane;
+                        cv[u][i] = c < kv_rank ? to_f(cs[(j + u) * kv_rank + c]) : 0.f;
+                        part[u] = fmaf(ql[i], cv[u][i], part[u]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < NR; ++i) {
+                        const int c = i * 32 + lane;
+                        if (c < rot_dim) part[u] = fmaf(qr[i], rs[(j + u) * rot_dim + c], part[u]);
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) part[u] += __shfl_xor_sync(0xffffffffu, part[u], o);
+                }
+                const float mn = fmaxf(fmaxf(fmaxf(m, part[0]), fmaxf(part[1], part[2])), part[3]);
+                const float alpha = expf(m - mn);
+                float p[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) p[u] = expf(part[u] - mn);
+                l = l * alpha + ((p[0] + p[1]) + (p[2] + p[3]));
+#pragma unroll
+                for (int i = 0; i < NC; ++i)
+                    acc[i] = acc[i] * alpha + ((p[0] * cv[0][i] + p[1] * cv[1][i]) + (p[2] * cv[2][i] + p[3] * cv[3][i]));
+                m = mn;
+            }
+            for (; j < kt; ++j) {
+                float cv[NC], part = 0.f;
 #pragma unroll
                 for (int i = 0; i < NC; ++i) {
                     const int c = i * 32 + lane;
-                    cv[u][i] = c < kv_rank ? to_f(cp[(size_t)(j + u) * kv_rank + c]) : 0.f;
-                    part[u] = fmaf(ql[i], cv[u][i], part[u]);
+                    cv[i] = c < kv_rank ? to_f(cs[j * kv_rank + c]) : 0.f;
+                    part = fmaf(ql[i], cv[i], part);
                 }
 #pragma unroll
                 for (int i = 0; i < NR; ++i) {
                     const int c = i * 32 + lane;
-                    if (c < rot_dim) part[u] = fmaf(qr[i], rp[(size_t)(j + u) * rot_dim + c], part[u]);
+                    if (c < rot_dim) part = fmaf(qr[i], rs[j * rot_dim + c], part);
                 }
+                const float sc = warp_sum(part);
+                const float mn = fmaxf(m, sc);
+                const float alpha = expf(m - mn), p = expf(sc - mn);
+                l = l * alpha + p;
+#pragma unroll
+                for (int i = 0; i < NC; ++i) acc[i] = acc[i] * alpha + p * cv[i];
+                m = mn;
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-                for (int u = 0; u < 4; ++u) part[u] += __shfl_xor_sync(0xffffffffu, part[u], o);
-            }
-            const float mn = fmaxf(fmaxf(fmaxf(m, part[0]), fmaxf(part[1], part[2])), part[3]);
-            const float alpha = expf(m - mn);
-            float p[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) p[u] = expf(part[u] - mn);
-            l = l * alpha + ((p[0] + p[1]) + (p[2] + p[3]));
-#pragma unroll
-            for (int i = 0; i < NC; ++i)
-                acc[i] = acc[i] * alpha + ((p[0] * cv[0][i] + p[1] * cv[1][i]) + (p[2] * cv[2][i] + p[3] * cv[3][i]));
-            m = mn;
-        }
-        for (; j < cnt; ++j) {
-            float cv[NC], part = 0.f;
-#pragma unroll
-            for (int i = 0; i < NC; ++i) {
-                const int c = i * 32 + lane;
-                cv[i] = c < kv_rank ? to_f(cp[(size_t)j * kv_rank + c]) : 0.f;
-                part = fmaf(ql[i], cv[i], part);
-            }
-#pragma unroll
-            for (int i = 0; i < NR; ++i) {
-                const int c = i * 32 + lane;
-                if (c < rot_dim) part = fmaf(qr[i], rp[(size_t)j * rot_dim + c], part);
-            }
-            const float sc = warp_sum(part);
-            const float mn = fmaxf(m, sc);
-            const float alpha = expf(m - mn), p = expf(sc - mn);
-            l = l * alpha + p;
-#pragma unroll
-            for (int i = 0; i < NC; ++i) acc[i] = acc[i] * alpha + p * cv[i];
-            m = mn;
         }
     }
+    if (!live) return;
     const size_t at = ((size_t)t * heads + h) * splits + z;
     float* out = o_lat + at * kv_rank;
 #pragma unroll
@@ -528,18 +558,30 @@ __global__ void expert_rows_kernel(const T* __restrict__ x, int x_div, const T* 
             const T* ra = wae + (size_t)r * K;
             const T* rb = DUAL ? wbe + (size_t)r * K : nullptr;
             if (VEC) {
-                for (int i = lane * P; i < K; i += 32 * P) {
-                    float va[P], vb[P];
-                    load_pack<T>(ra + i, va);
-                    if (DUAL) load_pack<T>(rb + i, vb);
+                // two 16-byte pieces of the row (and of its twin) are requested before either is used
+                for (int i = lane * P; i < K; i += 64 * P) {
+                    const int i1 = i + 32 * P;
+                    const bool two = i1 < K;
+                    float va[2][P], vb[2][P];
+                    load_pack<T>(ra + i, va[0]);
+                    if (DUAL) load_pack<T>(rb + i, vb[0]);
+                    if (two) {
+                        load_pack<T>(ra + i1, va[1]);
+                        if (DUAL) load_pack<T>(rb + i1, vb[1]);
+                    }
 #pragma unroll
-                    for (int u = 0; u < kExpertTile; ++u) {
-                        float xv[P];
-                        load_pack<T>(xs + (size_t)u * K + i, xv);
+                    for (int half = 0; half < 2; ++half) {
+                        if (half == 1 && !two) break;
+                        const int at = half ? i1 : i;
 #pragma unroll
-                        for (int k = 0; k < P; ++k) {
-                            a[u] = fmaf(va[k], xv[k], a[u]);
-                            if (DUAL) b[u] = fmaf(vb[k], xv[k], b[u]);
+                        for (int u = 0; u < kExpertTile; ++u) {
+                            float xv[P];
+                            load_pack<T>(xs + (size_t)u * K + at, xv);
+#pragma unroll
+                            for (int k = 0; k < P; ++k) {
+                                a[u] = fmaf(va[half][k], xv[k], a[u]);
+                                if (DUAL) b[u] = fmaf(vb[half][k], xv[k], b[u]);
+                            }
                         }
                     }
                 }
@@ -738,11 +780,12 @@ B200H_API int b200h_latent_prep(const b200h_latent_args* a)
 template <typename T>
 static int launch_latent_attention(const b200h_latent_args* a, cudaStream_t st)
 {
-    const int hpb = a->heads < 4 ? a->heads : 4;
+    const int hpb = a->heads < 8 ? a->heads : 8;
     const dim3 grid(a->n, (a->heads + hpb - 1) / hpb, a->splits), block(32, hpb);
+    const size_t tile = (size_t)(kKeyTile * a->kv_rank * sizeof(T) + 15) / 16 * 16 + (size_t)kKeyTile * a->rot_dim * sizeof(float);
     const int nc = (a->kv_rank + 31) / 32, nr = (a->rot_dim + 31) / 32;
 #define B200H_ATT(NC, NR)                                                                                                          \
-    latent_attention_kernel<T, NC, NR><<<grid, block, 0, st>>>((const float*)a->q_lat, (const float*)a->q_rot, (const float*)a->sink, \
+    latent_attention_kernel<T, NC, NR><<<grid, block, tile, st>>>((const float*)a->q_lat, (const float*)a->q_rot, (const float*)a->sink, \
         a->heads, a->kv_rank, a->rot_dim, (const int*)a->tok_seq, (const int*)a->tok_pos, (const int64_t*)a->block_ptrs,            \
         (const int*)a->cu_blocks, a->layer_off, a->block_len, a->rot_off, a->splits, (float*)a->o_lat, (float*)a->ml)
 #define B200H_ATT_R(NC)                                    \
