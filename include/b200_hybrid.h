@@ -48,17 +48,13 @@ typedef struct b200h_latent_args {
     void* cq;                /* T [n, q_rank]: out of b200h_latent_prep */
     const void* q;           /* T [n, ld_q]: per head dim plain then rot_dim rotated columns */
     int64_t ld_q;
-    const void* uk;          /* T [heads * dim, kv_rank] */
-    const void* uv;          /* T [heads * vdim, kv_rank] */
     const void* sink;        /* float [heads] */
-    const void* gate;        /* T [n, ld_gate]: heads * vdim columns, before the sigmoid */
-    int64_t ld_gate;
-    void* q_lat;             /* float [n, heads, kv_rank] scratch */
-    void* q_rot;             /* float [n, heads, rot_dim] scratch */
+    const void* q_lat;       /* float [n, heads, kv_rank]: the plain query parts carried into the latent's coordinates (uk_h^T q) */
+    void* q_rot;             /* float [n, heads, rot_dim]: out of b200h_rotate_query */
     void* o_lat;             /* float [n, heads, splits, kv_rank] scratch: unnormalised partial of every key range */
     void* ml;                /* float [n, heads, splits, 2] scratch: running maximum and denominator of every key range */
     int splits;              /* key ranges per row (whole pages each), >= 1 */
-    void* y;                 /* T [n, heads * vdim]: gated heads, the output projection's input */
+    void* o_heads;           /* T [heads, n, kv_rank]: out of b200h_latent_attention, the normalised weighted sum of latents */
     const void* tok_seq;     /* int [n] */
     const void* tok_pos;     /* int [n] */
     const void* block_ptrs;  /* int64: page addresses, entry s's pages from cu_blocks[s] */
@@ -91,8 +87,12 @@ B200H_API int b200h_depth_mix(void* x, void* hist, int64_t hist_stride, const vo
 
 /* Norm of both latents, rotation of the shared key part, cache store (fills cq). */
 B200H_API int b200h_latent_prep(const b200h_latent_args* args);
-/* Queries into latent coordinates, causal attention over the cache with the sink, value expansion and output gate (fills y). */
+/* Rotation of the per-head rotated query parts (fills q_rot). */
+B200H_API int b200h_rotate_query(const b200h_latent_args* args);
+/* Causal attention over the cached latents with the sink: score = scale * (q_lat . c + q_rot . kr) (fills o_heads). */
 B200H_API int b200h_latent_attention(const b200h_latent_args* args);
+/* y[t, h * vdim + v] = o[h, t, v] * sigmoid(gate[t, h * vdim + v]) as T; o float [heads, n, vdim] (the expanded values). */
+B200H_API int b200h_head_gate(const void* o, const void* gate, int64_t ld_gate, int n, int heads, int vdim, void* y, int dtype, void* stream);
 
 /* Per head S <- decay S + silu(k) silu(v)^T, out = S^T silu(q) (float [n, heads, vdim]); q, k, v are T with row stride ld;
  * state float [heads, vdim, dim] at state + seq_slot[s] * slot_stride, read and advanced. */

@@ -20,10 +20,9 @@ class LatentArgs(C.Structure):
         ("q_rank", C.c_int), ("block_len", C.c_int), ("scale", C.c_float), ("eps", C.c_float), ("rot", Rotary),
         ("dq", C.c_void_p), ("ld_dq", C.c_int64), ("dkv", C.c_void_p), ("ld_dkv", C.c_int64),
         ("q_norm", C.c_void_p), ("kv_norm", C.c_void_p), ("cq", C.c_void_p),
-        ("q", C.c_void_p), ("ld_q", C.c_int64), ("uk", C.c_void_p), ("uv", C.c_void_p), ("sink", C.c_void_p),
-        ("gate", C.c_void_p), ("ld_gate", C.c_int64),
+        ("q", C.c_void_p), ("ld_q", C.c_int64), ("sink", C.c_void_p),
         ("q_lat", C.c_void_p), ("q_rot", C.c_void_p), ("o_lat", C.c_void_p), ("ml", C.c_void_p), ("splits", C.c_int),
-        ("y", C.c_void_p),
+        ("o_heads", C.c_void_p),
         ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("block_ptrs", C.c_void_p), ("cu_blocks", C.c_void_p),
         ("layer_off", C.c_int64), ("rot_off", C.c_int64), ("dtype", C.c_int), ("stream", C.c_void_p),
     ]
@@ -60,6 +59,8 @@ def load():
     lib.b200h_depth_mix.argtypes = [P, P, L64, P, I, L64, P]
     lib.b200h_latent_prep.argtypes = [C.POINTER(LatentArgs)]
     lib.b200h_latent_attention.argtypes = [C.POINTER(LatentArgs)]
+    lib.b200h_rotate_query.argtypes = [C.POINTER(LatentArgs)]
+    lib.b200h_head_gate.argtypes = [P, P, L64, I, I, I, P, I, P]
     lib.b200h_decay_attention.argtypes = [P, P, P, L64, P, P, L64, P, P, I, I, I, I, P, I, P]
     lib.b200h_gated_rms.argtypes = [P, P, P, L64, I, I, F, P, I, P]
     lib.b200h_route.argtypes = [P, P, I, I, I, I, P, P, P]

@@ -201,34 +201,21 @@ __global__ void latent_prep_kernel(const T* __restrict__ dq, int64_t ld_dq, int 
     for (int i = 2 * rot.pairs + threadIdx.x; i < rot_dim; i += blockDim.x) r_dst[i] = to_f(kr[i]);
 }
 
-// Queries in the latent's coordinates: q_lat[t, h, :] = scale * uk_h^T q_plain[t, h, :] (so that q_lat . c == q_plain . (uk_h c)),
-// q_rot[t, h, :] = scale * rotated part.  One block per (row, head).
+// The rotated part of every head's query, rotated: q_rot[t, h, :] (float).  The plain part is carried into the latent's
+// coordinates by a batched GEMM (q_lat[t, h, :] = uk_h^T q_plain[t, h, :], so that q_lat . c == q_plain . (uk_h c) and no per-head
+// key is ever materialised); the attention kernel applies the score scale.
 template <typename T>
-__global__ void latent_query_kernel(const T* __restrict__ q, int64_t ld_q, const T* __restrict__ uk, int heads, int dim, int rot_dim,
-                                    int kv_rank, float scale, Rotary rot, const int* __restrict__ tok_pos,
-                                    float* __restrict__ q_lat, float* __restrict__ q_rot)
+__global__ void rotate_query_kernel(const T* __restrict__ q, int64_t ld_q, int heads, int dim, int rot_dim, Rotary rot,
+                                    const int* __restrict__ tok_pos, float* __restrict__ q_rot)
 {
-    extern __shared__ float sm[];
-    const int t = blockIdx.x, h = blockIdx.y, pos = tok_pos[t];
-    const T* qh = q + (size_t)t * ld_q + (size_t)h * (dim + rot_dim);
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) sm[d] = to_f(qh[d]);
-    __syncthreads();
-    const T* ukh = uk + (size_t)h * dim * kv_rank;
-    float* ql = q_lat + ((size_t)t * heads + h) * kv_rank;
-    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
-        float acc = 0.f;
-        for (int d = 0; d < dim; ++d) acc = fmaf(sm[d], to_f(ukh[(size_t)d * kv_rank + c]), acc);
-        ql[c] = acc * scale;
+    const int t = blockIdx.x, pos = tok_pos[t];
+    for (int h = threadIdx.y; h < heads; h += blockDim.y) {
+        const T* qr = q + (size_t)t * ld_q + (size_t)h * (dim + rot_dim) + dim;
+        float* out = q_rot + ((size_t)t * heads + h) * rot_dim;
+        for (int i = threadIdx.x; i < rot.pairs; i += blockDim.x)
+            rotate_pair(to_f(qr[2 * i]), to_f(qr[2 * i + 1]), pos, rot.freqs[i], rot.magnitude, out[2 * i], out[2 * i + 1]);
+        for (int i = 2 * rot.pairs + threadIdx.x; i < rot_dim; i += blockDim.x) out[i] = to_f(qr[i]);
     }
-    const T* qr = qh + dim;
-    float* out = q_rot + ((size_t)t * heads + h) * rot_dim;
-    for (int i = threadIdx.x; i < rot.pairs; i += blockDim.x) {
-        float a, b;
-        rotate_pair(to_f(qr[2 * i]), to_f(qr[2 * i + 1]), pos, rot.freqs[i], rot.magnitude, a, b);
-        out[2 * i] = a * scale;
-        out[2 * i + 1] = b * scale;
-    }
-    for (int i = 2 * rot.pairs + threadIdx.x; i < rot_dim; i += blockDim.x) out[i] = to_f(qr[i]) * scale;
 }
 
 // Causal attention of one (row, head, key range) per warp over the cached latents: score_j = q_lat . c_j + q_rot . kr_j, online
@@ -259,7 +246,7 @@ __global__ void __launch_bounds__(256, 2) latent_attention_kernel(const float* _
                                         int heads, int kv_rank, int rot_dim, const int* __restrict__ tok_seq,
                                         const int* __restrict__ tok_pos, const int64_t* __restrict__ block_ptrs,
                                         const int* __restrict__ cu_blocks, int64_t layer_off, int block_len, int64_t rot_off,
-                                        int splits, float* __restrict__ o_lat, float* __restrict__ ml)
+                                        int splits, float scale, float* __restrict__ o_lat, float* __restrict__ ml)
 {
     extern __shared__ __align__(16) unsigned char tile_raw[];
     const int c_row = kv_rank * (int)sizeof(T), r_row = rot_dim * (int)sizeof(float);
@@ -315,6 +302,8 @@ __global__ void __launch_bounds__(256, 2) latent_attention_kernel(const float* _
 #pragma unroll
                     for (int u = 0; u < 4; ++u) part[u] += __shfl_xor_sync(0xffffffffu, part[u], o);
                 }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) part[u] *= scale;
                 const float mn = fmaxf(fmaxf(fmaxf(m, part[0]), fmaxf(part[1], part[2])), part[3]);
                 const float alpha = expf(m - mn);
                 float p[4];
@@ -339,7 +328,7 @@ __global__ void __launch_bounds__(256, 2) latent_attention_kernel(const float* _
                     const int c = i * 32 + lane;
                     if (c < rot_dim) part = fmaf(qr[i], rs[j * rot_dim + c], part);
                 }
-                const float sc = warp_sum(part);
+                const float sc = warp_sum(part) * scale;
                 const float mn = fmaxf(m, sc);
                 const float alpha = expf(m - mn), p = expf(sc - mn);
                 l = l * alpha + p;
@@ -357,14 +346,13 @@ __global__ void __launch_bounds__(256, 2) latent_attention_kernel(const float* _
     if (lane == 0) { ml[2 * at] = m; ml[2 * at + 1] = l; }
 }
 
-// Merge of the key ranges' partials, value expansion and gate:
-// y[t, h*vdim + v] = (uv_h o_lat[t, h])[v] * sigmoid(gate[t, h*vdim + v]) as T.  One block per (row, head), a warp per value row.
+// Merge of the key ranges' partials into the normalised weighted latent sum, stored as T head-major [heads, n, kv_rank]: the
+// operand of the batched GEMM that expands it to values (o[h] = o_lat[h] uv_h^T).
 template <typename T>
-__global__ void latent_out_kernel(const float* __restrict__ o_lat, const float* __restrict__ ml, int splits, const T* __restrict__ uv,
-                                  const T* __restrict__ gate, int64_t ld_gate, int heads, int vdim, int kv_rank, T* __restrict__ y)
+__global__ void latent_merge_kernel(const float* __restrict__ o_lat, const float* __restrict__ ml, int splits, int n, int heads,
+                                    int kv_rank, T* __restrict__ out)
 {
-    extern __shared__ float sm[];
-    const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int t = blockIdx.x, h = blockIdx.y;
     const size_t at = ((size_t)t * heads + h) * splits;
     float top = ml[2 * at];
     for (int z = 1; z < splits; ++z) top = fmaxf(top, ml[2 * (at + z)]);
@@ -374,18 +362,19 @@ __global__ void latent_out_kernel(const float* __restrict__ o_lat, const float* 
     for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
         float v = 0.f;
         for (int z = 0; z < splits; ++z) v += expf(ml[2 * (at + z)] - top) * o_lat[(at + z) * kv_rank + c];
-        sm[c] = v * inv;
+        out[((size_t)h * n + t) * kv_rank + c] = from_f<T>(v * inv);
     }
-    __syncthreads();
-    for (int v = warp; v < vdim; v += nw) {
-        const T* row = uv + ((size_t)h * vdim + v) * kv_rank;
-        float part = 0.f;
-        for (int c = lane; c < kv_rank; c += 32) part = fmaf(to_f(row[c]), sm[c], part);
-        part = warp_sum(part);
-        if (lane == 0) {
-            const size_t col = (size_t)h * vdim + v;
-            y[(size_t)t * heads * vdim + col] = from_f<T>(part * sigmoid_f(to_f(gate[(size_t)t * ld_gate + col])));
-        }
+}
+
+// y[t, h*vdim + v] = o[h, t, v] * sigmoid(gate[t, h*vdim + v]) as T; o float head-major [heads, n, vdim].
+template <typename T>
+__global__ void head_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int64_t ld_gate, int n, int heads, int vdim,
+                                 T* __restrict__ y)
+{
+    const int t = blockIdx.x, cols = heads * vdim;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        const int h = i / vdim, v = i - h * vdim;
+        y[(size_t)t * cols + i] = from_f<T>(o[((size_t)h * n + t) * vdim + v] * sigmoid_f(to_f(gate[(size_t)t * ld_gate + i])));
     }
 }
 
@@ -558,29 +547,30 @@ __global__ void expert_rows_kernel(const T* __restrict__ x, int x_div, const T* 
             const T* ra = wae + (size_t)r * K;
             const T* rb = DUAL ? wbe + (size_t)r * K : nullptr;
             if (VEC) {
-                // two 16-byte pieces of the row (and of its twin) are requested before either is used
-                for (int i = lane * P; i < K; i += 64 * P) {
-                    const int i1 = i + 32 * P;
-                    const bool two = i1 < K;
-                    float va[2][P], vb[2][P];
-                    load_pack<T>(ra + i, va[0]);
-                    if (DUAL) load_pack<T>(rb + i, vb[0]);
-                    if (two) {
-                        load_pack<T>(ra + i1, va[1]);
-                        if (DUAL) load_pack<T>(rb + i1, vb[1]);
+                // four 16-byte pieces of the row (and of its twin) are requested before any is used
+                for (int i = lane * P; i < K; i += 128 * P) {
+                    float va[4][P], vb[4][P];
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const int at = i + q4 * 32 * P;
+                        if (at < K) {
+                            load_pack<T>(ra + at, va[q4]);
+                            if (DUAL) load_pack<T>(rb + at, vb[q4]);
+                        }
                     }
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        if (half == 1 && !two) break;
-                        const int at = half ? i1 : i;
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const int at = i + q4 * 32 * P;
+                        if (at < K) {
 #pragma unroll
-                        for (int u = 0; u < kExpertTile; ++u) {
-                            float xv[P];
-                            load_pack<T>(xs + (size_t)u * K + at, xv);
+                            for (int u = 0; u < kExpertTile; ++u) {
+                                float xv[P];
+                                load_pack<T>(xs + (size_t)u * K + at, xv);
 #pragma unroll
-                            for (int k = 0; k < P; ++k) {
-                                a[u] = fmaf(va[half][k], xv[k], a[u]);
-                                if (DUAL) b[u] = fmaf(vb[half][k], xv[k], b[u]);
+                                for (int k = 0; k < P; ++k) {
+                                    a[u] = fmaf(va[q4][k], xv[k], a[u]);
+                                    if (DUAL) b[u] = fmaf(vb[q4][k], xv[k], b[u]);
+                                }
                             }
                         }
                     }
@@ -787,7 +777,7 @@ static int launch_latent_attention(const b200h_latent_args* a, cudaStream_t st)
 #define B200H_ATT(NC, NR)                                                                                                          \
     latent_attention_kernel<T, NC, NR><<<grid, block, tile, st>>>((const float*)a->q_lat, (const float*)a->q_rot, (const float*)a->sink, \
         a->heads, a->kv_rank, a->rot_dim, (const int*)a->tok_seq, (const int*)a->tok_pos, (const int64_t*)a->block_ptrs,            \
-        (const int*)a->cu_blocks, a->layer_off, a->block_len, a->rot_off, a->splits, (float*)a->o_lat, (float*)a->ml)
+        (const int*)a->cu_blocks, a->layer_off, a->block_len, a->rot_off, a->splits, a->scale, (float*)a->o_lat, (float*)a->ml)
 #define B200H_ATT_R(NC)                                    \
     if (nr <= 1) B200H_ATT(NC, 1);                         \
     else if (nr <= 2) B200H_ATT(NC, 2);                    \
@@ -802,23 +792,40 @@ static int launch_latent_attention(const b200h_latent_args* a, cudaStream_t st)
     return 0;
 }
 
+B200H_API int b200h_rotate_query(const b200h_latent_args* a)
+{
+    if (!a || !a->q || !a->q_rot || !a->tok_pos) return fail(B200H_ERR_INVALID_ARG, "rotate_query: bad arguments");
+    if (2 * a->rot.pairs > a->rot_dim) return fail(B200H_ERR_INVALID_ARG, "rotate_query: more rotated pairs than rot_dim holds");
+    if (a->n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)a->stream;
+    B200H_DISPATCH_T(a->dtype, rotate_query_kernel<T><<<a->n, dim3(32, 8), 0, st>>>((const T*)a->q, a->ld_q, a->heads, a->dim, a->rot_dim,
+                                                                                   make_rotary(&a->rot), (const int*)a->tok_pos,
+                                                                                   (float*)a->q_rot));
+    return launched("rotate_query");
+}
+
 B200H_API int b200h_latent_attention(const b200h_latent_args* a)
 {
-    if (!a || !a->q || !a->uk || !a->uv || !a->gate || !a->sink || !a->q_lat || !a->q_rot || !a->o_lat || !a->y || !a->block_ptrs ||
-        !a->tok_seq || !a->tok_pos || !a->cu_blocks || !a->ml || a->splits < 1 || a->splits > 65535)
+    if (!a || !a->sink || !a->q_lat || !a->q_rot || !a->o_lat || !a->o_heads || !a->block_ptrs || !a->tok_seq || !a->tok_pos ||
+        !a->cu_blocks || !a->ml || a->splits < 1 || a->splits > 65535)
         return fail(B200H_ERR_INVALID_ARG, "latent_attention: bad arguments");
     if (a->kv_rank > 512 || a->rot_dim > 128) return fail(B200H_ERR_UNSUPPORTED, "latent_attention: kv_rank <= 512 and rot_dim <= 128");
     if (a->n == 0) return 0;
     cudaStream_t st = (cudaStream_t)a->stream;
-    const dim3 rows_heads(a->n, a->heads);
-    B200H_DISPATCH_T(a->dtype, latent_query_kernel<T><<<rows_heads, 128, a->dim * sizeof(float), st>>>(
-        (const T*)a->q, a->ld_q, (const T*)a->uk, a->heads, a->dim, a->rot_dim, a->kv_rank, a->scale, make_rotary(&a->rot),
-        (const int*)a->tok_pos, (float*)a->q_lat, (float*)a->q_rot));
     B200H_DISPATCH_T(a->dtype, launch_latent_attention<T>(a, st));
-    B200H_DISPATCH_T(a->dtype, latent_out_kernel<T><<<rows_heads, 128, a->kv_rank * sizeof(float), st>>>(
-        (const float*)a->o_lat, (const float*)a->ml, a->splits, (const T*)a->uv, (const T*)a->gate, a->ld_gate, a->heads, a->vdim, a->kv_rank,
-        (T*)a->y));
+    B200H_DISPATCH_T(a->dtype, latent_merge_kernel<T><<<dim3(a->n, a->heads), 128, 0, st>>>((const float*)a->o_lat, (const float*)a->ml,
+                                                                                           a->splits, a->n, a->heads, a->kv_rank,
+                                                                                           (T*)a->o_heads));
     return launched("latent_attention");
+}
+
+B200H_API int b200h_head_gate(const void* o, const void* gate, int64_t ld_gate, int n, int heads, int vdim, void* y, int dtype, void* stream)
+{
+    if (!o || !gate || !y || heads <= 0 || vdim <= 0) return fail(B200H_ERR_INVALID_ARG, "head_gate: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, head_gate_kernel<T><<<n, 256, 0, st>>>((const float*)o, (const T*)gate, ld_gate, n, heads, vdim, (T*)y));
+    return launched("head_gate");
 }
 
 B200H_API int b200h_decay_attention(const void* q, const void* k, const void* v, int64_t ld, const void* decay, void* state,

@@ -339,7 +339,7 @@ class HybridModel:
         a.rot = H.Rotary(w[p + "freqs"].data_ptr(), m.rot.dims // 2, w[p + "mag"])
         a.dq, a.ld_dq = proj.data_ptr(), ld
         a.dkv, a.ld_dkv = proj.data_ptr() + es * m.q_rank, ld
-        a.gate, a.ld_gate = proj.data_ptr() + es * (m.q_rank + m.kv_rank + m.rot_dim), ld
+        gate = proj.data_ptr() + es * (m.q_rank + m.kv_rank + m.rot_dim)
         a.q_norm, a.kv_norm, a.sink = w[p + "dq.norm"].data_ptr(), w[p + "dkv.norm"].data_ptr(), w[p + "sink"].data_ptr()
         cq = torch.empty(n, m.q_rank, dtype=T, device=dev)
         a.cq = cq.data_ptr()
@@ -350,20 +350,39 @@ class HybridModel:
             H.check(lib.b200h_latent_prep(C.byref(a)), "latent_prep")
         with self.timed("gemm query up"):
             q = self._linear(cq, w[p + "uq"])
-        q_lat = torch.empty(n, m.heads, m.kv_rank, **f32)
+        a.q, a.ld_q = q.data_ptr(), q.stride(0)
         q_rot = torch.empty(n, m.heads, m.rot_dim, **f32)
+        a.q_rot = q_rot.data_ptr()
+        with self.timed("rotate query"):
+            H.check(lib.b200h_rotate_query(C.byref(a)), "rotate_query")
+        with self.timed("gemm query into latent"):
+            # q_lat[t, h] = uk_h^T q_plain[t, h]: one batched GEMM over the heads, float result
+            q_plain = q.view(n, m.heads, m.dim + m.rot_dim)[:, :, :m.dim].transpose(0, 1)
+            q_lat = self._bmm(q_plain, w[p + "uk"].view(m.heads, m.dim, m.kv_rank)).transpose(0, 1).contiguous()
         # key ranges per row: one for prompt portions (rows x heads already fill the SMs), several whole-page ranges when a step
         # of few rows would leave most SMs idle
         splits = self.attention_splits(n, m.heads, c.max_pos)
         o_lat = torch.empty(n, m.heads, splits, m.kv_rank, **f32)
         ml = torch.empty(n, m.heads, splits, 2, **f32)
-        a.ml, a.splits = ml.data_ptr(), splits
-        y = torch.empty(n, m.heads * m.vdim, dtype=T, device=dev)
-        a.q, a.ld_q, a.uk, a.uv = q.data_ptr(), q.stride(0), w[p + "uk"].data_ptr(), w[p + "uv"].data_ptr()
-        a.q_lat, a.q_rot, a.o_lat, a.y = q_lat.data_ptr(), q_rot.data_ptr(), o_lat.data_ptr(), y.data_ptr()
+        o_heads = torch.empty(m.heads, n, m.kv_rank, dtype=T, device=dev)
+        a.q_lat, a.o_lat, a.ml, a.splits, a.o_heads = q_lat.data_ptr(), o_lat.data_ptr(), ml.data_ptr(), splits, o_heads.data_ptr()
         with self.timed("latent attention"):
             H.check(lib.b200h_latent_attention(C.byref(a)), "latent_attention")
+        with self.timed("gemm latent into values"):
+            o = self._bmm(o_heads, w[p + "uv"].view(m.heads, m.vdim, m.kv_rank).transpose(1, 2))       # float [heads, n, vdim]
+        y = torch.empty(n, m.heads * m.vdim, dtype=T, device=dev)
+        with self.timed("output gate"):
+            H.check(lib.b200h_head_gate(o.data_ptr(), gate, ld, n, m.heads, m.vdim, y.data_ptr(), self.dt, self._stream()), "head_gate")
         return y
+
+    def _bmm(self, a, b):
+        """Batched product with a float result (bf16 operands accumulate and stay in float)."""
+        if self.T is torch.float32 or a.device.type != "cuda":
+            return torch.bmm(a.float(), b.float())
+        try:
+            return torch.bmm(a, b, out_dtype=torch.float32)
+        except RuntimeError:
+            return torch.bmm(a.float(), b.float())
 
     def decay_mixer(self, i, h, c):
         """Decayed linear attention of layer i: one stacked projection (q | k | v | gate), the per-head recurrence on the

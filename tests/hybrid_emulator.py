@@ -125,26 +125,35 @@ class EmulatedHybridLib:
             kr[:] = self._rot(dkv[t, a.kv_rank:], poss[t], a)
         return 0
 
+    def b200h_rotate_query(self, args):
+        a = args._obj
+        H, D, R = a.heads, a.dim, a.rot_dim
+        q = _rows(a.q, a.n, a.ld_q, H * (D + R)).reshape(a.n, H, D + R)
+        out, poss = _f(a.q_rot, a.n, H, R), _i(a.tok_pos, a.n)
+        for t in range(a.n):
+            out[t] = self._rot(q[t, :, D:], int(poss[t]), a)
+        return 0
+
     def b200h_latent_attention(self, args):
         a = args._obj
-        H, D, R, V, Ck = a.heads, a.dim, a.rot_dim, a.vdim, a.kv_rank
-        q = _rows(a.q, a.n, a.ld_q, H * (D + R)).reshape(a.n, H, D + R)
-        uk, uv, sink = _f(a.uk, H, D, Ck), _f(a.uv, H, V, Ck), _f(a.sink, H)
-        gate = _rows(a.gate, a.n, a.ld_gate, H * V)
-        y = _f(a.y, a.n, H * V)
+        H, R, Ck = a.heads, a.rot_dim, a.kv_rank
+        q_lat, q_rot, sink = _f(a.q_lat, a.n, H, Ck), _f(a.q_rot, a.n, H, R), _f(a.sink, H)
+        out = _f(a.o_heads, H, a.n, Ck)
         seqs, poss = _i(a.tok_seq, a.n), _i(a.tok_pos, a.n)
         for t in range(a.n):
             s, pos = int(seqs[t]), int(poss[t])
             cs, krs = zip(*[self._page(a, s, j) for j in range(pos + 1)])
             cs, krs = np.stack(cs), np.stack(krs)
-            q_rot = self._rot(q[t, :, D:], pos, a) * np.float32(a.scale)
             for h in range(H):
-                q_lat = (q[t, h, :D] @ uk[h]) * np.float32(a.scale)
-                sc = cs @ q_lat + krs @ q_rot[h]
+                sc = (cs @ q_lat[t, h] + krs @ q_rot[t, h]) * np.float32(a.scale)
                 top = max(float(sc.max()), float(sink[h]))
                 e = np.exp(sc - top)
-                o_lat = (e / (e.sum() + np.exp(sink[h] - top))) @ cs
-                y[t, h * V:(h + 1) * V] = (uv[h] @ o_lat) * _sigmoid(gate[t, h * V:(h + 1) * V])
+                out[h, t] = (e / (e.sum() + np.exp(sink[h] - top))) @ cs
+        return 0
+
+    def b200h_head_gate(self, o, gate, ld_gate, n, heads, vdim, y, dtype, stream):
+        O = _f(o, heads, n, vdim).transpose(1, 0, 2).reshape(n, heads * vdim)
+        _f(y, n, heads * vdim)[:] = O * _sigmoid(_rows(gate, n, ld_gate, heads * vdim))
         return 0
 
     def b200h_decay_attention(self, q, k, v, ld, decay, state, slot_stride, cu_q, seq_slot, batch, heads, dim, vdim, out, dtype, stream):
