@@ -221,12 +221,12 @@ __global__ void rotate_query_kernel(const T* __restrict__ q, int64_t ld_q, int h
 // Causal attention of one (row, head, key range) per warp over the cached latents: score_j = q_lat . c_j + q_rot . kr_j, online
 // softmax, o_lat = sum_j w_j c_j.  Lane l owns the latent coordinates l, l + 32, ...; a key's latent is loaded once and used for
 // the score and for the weighted sum; four keys are in flight per iteration (independent dot products and reductions).  The
-// warps of a block are heads of the same row: sixteen keys at a time are staged in shared memory once for all of them.
+// warps of a block are heads of the same row: thirty-two keys at a time are staged in shared memory once for all of them.
 // The keys of a row are cut into `splits` ranges of whole pages (blockIdx.z); range 0 starts its running maximum at the
 // sink (a term exp(sink_h) in the denominator with no value), the others empty.  Every range leaves an unnormalised partial
 // (max, denominator, weighted sum) that latent_out_kernel merges -- prompt portions run with one range, a step of single
 // decoded tokens with several, so that a few rows still fill the SMs.
-constexpr int kKeyTile = 16;           // keys staged in shared memory at a time, shared by the heads of the block
+constexpr int kKeyTile = 32;           // keys staged in shared memory at a time, shared by the heads of the block
 
 // Copy `bytes` (a multiple of `unit`) from global to shared memory with the whole block: 16-byte pieces when both allow it.
 __device__ __forceinline__ void stage(void* dst, const void* src, int bytes, int unit, int tid, int nthreads)
@@ -397,21 +397,41 @@ __global__ void decay_scan_kernel(const T* __restrict__ q, const T* __restrict__
 #pragma unroll
     for (int i = 0; i < NW; ++i) { const int d = i * 32 + lane; st[i] = d < dim ? sp[d] : 0.f; }
     const float lam = decay[h];
-    for (int t = first; t < last; ++t) {
-        const T* qt = q + (size_t)t * ld + (size_t)h * dim;
-        const T* kt = k + (size_t)t * ld + (size_t)h * dim;
-        const float vv = silu_f(to_f(v[(size_t)t * ld + (size_t)h * vdim + col]));
-        float part = 0.f;
+    // four rows at a time: their q, k, v loads and activations do not depend on the state, only the four updates are in order
+    for (int t0 = first; t0 < last; t0 += 4) {
+        float qa[4][NW], ka[4][NW], va[4];
 #pragma unroll
-        for (int i = 0; i < NW; ++i) {
-            const int d = i * 32 + lane;
-            if (d < dim) {
-                st[i] = fmaf(lam, st[i], silu_f(to_f(kt[d])) * vv);
-                part = fmaf(st[i], silu_f(to_f(qt[d])), part);
+        for (int u = 0; u < 4; ++u) {
+            const int t = min(t0 + u, last - 1);
+            const T* qt = q + (size_t)t * ld + (size_t)h * dim;
+            const T* kt = k + (size_t)t * ld + (size_t)h * dim;
+            va[u] = to_f(v[(size_t)t * ld + (size_t)h * vdim + col]);
+#pragma unroll
+            for (int i = 0; i < NW; ++i) {
+                const int d = i * 32 + lane;
+                qa[u][i] = d < dim ? to_f(qt[d]) : 0.f;
+                ka[u][i] = d < dim ? to_f(kt[d]) : 0.f;
             }
         }
-        part = warp_sum(part);
-        if (lane == 0) out[((size_t)t * heads + h) * vdim + col] = part;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            va[u] = silu_f(va[u]);
+#pragma unroll
+            for (int i = 0; i < NW; ++i) { qa[u][i] = silu_f(qa[u][i]); ka[u][i] = silu_f(ka[u][i]); }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (t0 + u < last) {
+                float part = 0.f;
+#pragma unroll
+                for (int i = 0; i < NW; ++i) {
+                    st[i] = fmaf(lam, st[i], ka[u][i] * va[u]);          // rows past dim hold zeros and stay zero
+                    part = fmaf(st[i], qa[u][i], part);
+                }
+                part = warp_sum(part);
+                if (lane == 0) out[((size_t)(t0 + u) * heads + h) * vdim + col] = part;
+            }
+        }
     }
 #pragma unroll
     for (int i = 0; i < NW; ++i) { const int d = i * 32 + lane; if (d < dim) sp[d] = st[i]; }
@@ -519,7 +539,7 @@ __device__ __forceinline__ void load_pack<float>(const float* p, float (&v)[4])
 }
 
 template <typename T, bool DUAL, bool VEC>
-__global__ void expert_rows_kernel(const T* __restrict__ x, int x_div, const T* __restrict__ wa, const T* __restrict__ wb,
+__global__ void __launch_bounds__(256, 3) expert_rows_kernel(const T* __restrict__ x, int x_div, const T* __restrict__ wa, const T* __restrict__ wb,
                                    const int* __restrict__ counts, const int* __restrict__ lists, int entries,
                                    const float* __restrict__ wts, int K, int R, void* __restrict__ out_)
 {
@@ -547,20 +567,20 @@ __global__ void expert_rows_kernel(const T* __restrict__ x, int x_div, const T* 
             const T* ra = wae + (size_t)r * K;
             const T* rb = DUAL ? wbe + (size_t)r * K : nullptr;
             if (VEC) {
-                // four 16-byte pieces of the row (and of its twin) are requested before any is used
-                for (int i = lane * P; i < K; i += 128 * P) {
-                    float va[4][P], vb[4][P];
+                // two 16-byte pieces of the row (and of its twin) are requested before either is used
+                for (int i = lane * P; i < K; i += 64 * P) {
+                    float va[2][P], vb[2][P];
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const int at = i + q4 * 32 * P;
+                    for (int q2 = 0; q2 < 2; ++q2) {
+                        const int at = i + q2 * 32 * P;
                         if (at < K) {
-                            load_pack<T>(ra + at, va[q4]);
-                            if (DUAL) load_pack<T>(rb + at, vb[q4]);
+                            load_pack<T>(ra + at, va[q2]);
+                            if (DUAL) load_pack<T>(rb + at, vb[q2]);
                         }
                     }
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const int at = i + q4 * 32 * P;
+                    for (int q2 = 0; q2 < 2; ++q2) {
+                        const int at = i + q2 * 32 * P;
                         if (at < K) {
 #pragma unroll
                             for (int u = 0; u < kExpertTile; ++u) {
@@ -568,8 +588,8 @@ __global__ void expert_rows_kernel(const T* __restrict__ x, int x_div, const T* 
                                 load_pack<T>(xs + (size_t)u * K + at, xv);
 #pragma unroll
                                 for (int k = 0; k < P; ++k) {
-                                    a[u] = fmaf(va[q4][k], xv[k], a[u]);
-                                    if (DUAL) b[u] = fmaf(vb[q4][k], xv[k], b[u]);
+                                    a[u] = fmaf(va[q2][k], xv[k], a[u]);
+                                    if (DUAL) b[u] = fmaf(vb[q2][k], xv[k], b[u]);
                                 }
                             }
                         }
@@ -775,9 +795,14 @@ static int launch_latent_attention(const b200h_latent_args* a, cudaStream_t st)
     const size_t tile = (size_t)(kKeyTile * a->kv_rank * sizeof(T) + 15) / 16 * 16 + (size_t)kKeyTile * a->rot_dim * sizeof(float);
     const int nc = (a->kv_rank + 31) / 32, nr = (a->rot_dim + 31) / 32;
 #define B200H_ATT(NC, NR)                                                                                                          \
-    latent_attention_kernel<T, NC, NR><<<grid, block, tile, st>>>((const float*)a->q_lat, (const float*)a->q_rot, (const float*)a->sink, \
-        a->heads, a->kv_rank, a->rot_dim, (const int*)a->tok_seq, (const int*)a->tok_pos, (const int64_t*)a->block_ptrs,            \
-        (const int*)a->cu_blocks, a->layer_off, a->block_len, a->rot_off, a->splits, a->scale, (float*)a->o_lat, (float*)a->ml)
+    do {                                                                                                                           \
+        if (tile > 48 * 1024)                                                                                                      \
+            cudaFuncSetAttribute(latent_attention_kernel<T, NC, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile);      \
+        latent_attention_kernel<T, NC, NR><<<grid, block, tile, st>>>((const float*)a->q_lat, (const float*)a->q_rot,              \
+            (const float*)a->sink, a->heads, a->kv_rank, a->rot_dim, (const int*)a->tok_seq, (const int*)a->tok_pos,               \
+            (const int64_t*)a->block_ptrs, (const int*)a->cu_blocks, a->layer_off, a->block_len, a->rot_off, a->splits, a->scale,  \
+            (float*)a->o_lat, (float*)a->ml);                                                                                      \
+    } while (0)
 #define B200H_ATT_R(NC)                                    \
     if (nr <= 1) B200H_ATT(NC, 1);                         \
     else if (nr <= 2) B200H_ATT(NC, 2);                    \
