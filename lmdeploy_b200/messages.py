@@ -221,7 +221,7 @@ class TurbomindEngineConfig:
     language_model_only: bool = False
 
     def __post_init__(self):
-        if self.dtype not in ("auto", "float16", "bfloat16", "float32"):      # float32: hybrid decoders only (turbomind/loader.py)
+        if self.dtype not in ("auto", "float16", "bfloat16"):
             raise ConfigError(f"unsupported dtype {self.dtype}")
         if self.tp < 1 or (self.tp & (self.tp - 1)):
             raise ConfigError("tp must be a power of two >= 1")

@@ -161,10 +161,12 @@ class TurboMind:
         self._hybrid_graphs, self._hybrid_seen = {}, set()
 
     @classmethod
-    def from_pretrained(cls, pretrained_model_name_or_path, engine_config=None, **kw):
+    def from_pretrained(cls, pretrained_model_name_or_path, engine_config=None, *, dtype=None, **kw):
         """`pretrained_model_name_or_path`: a key of SPECS (synthetic random weights of that geometry; no real
         checkpoints exist in this image) or a directory holding an HF-format checkpoint (config.json +
-        *.safetensors, InternLM2 / Llama, fp16 or AWQ) read by lmdeploy_b200.turbomind.loader."""
+        *.safetensors, InternLM2 / Llama, fp16 or AWQ; or a hybrid decoder named by the config's `architecture`) read by
+        lmdeploy_b200.turbomind.loader.  dtype: overrides engine_config.dtype for the loader; 'float32' (true 32-bit serving) is
+        offered by hybrid decoders only and is not a value of TurbomindEngineConfig.dtype, whose rules are the reference's."""
         import os
         if pretrained_model_name_or_path in SPECS:
             return cls(SPECS[pretrained_model_name_or_path], engine_config, **kw)
@@ -174,7 +176,7 @@ class TurboMind:
             spec, model, eos = load_hf_checkpoint(pretrained_model_name_or_path, quant_policy=cfg.quant_policy,
                                                   block_len=cfg.cache_block_seq_len, hf_overrides=cfg.hf_overrides,
                                                   model_format=cfg.model_format,
-                                                  max_batch=cfg.max_batch_size or DEFAULT_MAX_BATCH_SIZE, dtype=cfg.dtype)
+                                                  max_batch=cfg.max_batch_size or DEFAULT_MAX_BATCH_SIZE, dtype=dtype or cfg.dtype)
             return cls(spec, cfg, model=model, eos_id=eos, **kw)
         raise FileNotFoundError(pretrained_model_name_or_path)
 

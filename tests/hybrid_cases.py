@@ -88,7 +88,7 @@ def build_engine(cfg, tensors, *, device, dtype="f32", blocks=8, max_batch=4, em
     finally:
         H.load = real
     model.load_weights(lambda k: tensors[k])
-    ecfg = TurbomindEngineConfig(dtype="float32" if dtype == "f32" else "bfloat16", cache_max_entry_count=blocks, max_batch_size=max_batch,
+    ecfg = TurbomindEngineConfig(cache_max_entry_count=blocks, max_batch_size=max_batch,
                                  session_len=blocks * BLOCK + 1, max_prefill_token_num=prefill_tokens or blocks * BLOCK)
     return TurboMind(spec, ecfg, model=model)
 

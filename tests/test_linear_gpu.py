@@ -234,6 +234,10 @@ def test_fused_residual_rmsnorm_epilogue(lib, shape, m):
     rc = lib.b200_linear_forward_packed_residual_rmsnorm(C.byref(lin.d), xp.data_ptr(), mt, m, d_res.data_ptr(),
                                                          d_nw.data_ptr(), C.c_float(1e-5), out.data_ptr(), 0,
                                                          lin.ws.data_ptr(), lin.ws.numel(), st)
+    if rc == L.ERR_UNSUPPORTED:
+        # the fused epilogue needs the launch plan's split-K exchange; for a shape whose plan has no split the library says so
+        # and the step driver keeps the separate residual + RMSNorm kernel (the fused form is off by default)
+        pytest.skip(lib.b200_last_error().decode())
     L.check(rc, "b200_linear_forward_packed_residual_rmsnorm")
     torch.cuda.synchronize()
     y = OL.linear(x, OL.dequant_u4(q, s, z, F16), F16)
