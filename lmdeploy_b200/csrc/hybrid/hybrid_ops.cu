@@ -402,22 +402,26 @@ __global__ void decay_scan_kernel(const T* __restrict__ q, const T* __restrict__
         float qa[4][NW], ka[4][NW], va[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int t = min(t0 + u, last - 1);
-            const T* qt = q + (size_t)t * ld + (size_t)h * dim;
-            const T* kt = k + (size_t)t * ld + (size_t)h * dim;
-            va[u] = to_f(v[(size_t)t * ld + (size_t)h * vdim + col]);
+            if (t0 + u < last) {                      // a step of one row (decode) loads and activates one row
+                const int t = t0 + u;
+                const T* qt = q + (size_t)t * ld + (size_t)h * dim;
+                const T* kt = k + (size_t)t * ld + (size_t)h * dim;
+                va[u] = to_f(v[(size_t)t * ld + (size_t)h * vdim + col]);
 #pragma unroll
-            for (int i = 0; i < NW; ++i) {
-                const int d = i * 32 + lane;
-                qa[u][i] = d < dim ? to_f(qt[d]) : 0.f;
-                ka[u][i] = d < dim ? to_f(kt[d]) : 0.f;
+                for (int i = 0; i < NW; ++i) {
+                    const int d = i * 32 + lane;
+                    qa[u][i] = d < dim ? to_f(qt[d]) : 0.f;
+                    ka[u][i] = d < dim ? to_f(kt[d]) : 0.f;
+                }
             }
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            va[u] = silu_f(va[u]);
+            if (t0 + u < last) {
+                va[u] = silu_f(va[u]);
 #pragma unroll
-            for (int i = 0; i < NW; ++i) { qa[u][i] = silu_f(qa[u][i]); ka[u][i] = silu_f(ka[u][i]); }
+                for (int i = 0; i < NW; ++i) { qa[u][i] = silu_f(qa[u][i]); ka[u][i] = silu_f(ka[u][i]); }
+            }
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -957,7 +961,7 @@ B200H_API int b200h_argmax(const void* logits, int64_t ld, int rows, int vocab, 
 {
     if (!logits || !out || vocab <= 0) return fail(B200H_ERR_INVALID_ARG, "argmax: bad arguments");
     if (rows == 0) return 0;
-    argmax_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((const float*)logits, ld, vocab, (int*)out);
+    argmax_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>((const float*)logits, ld, vocab, (int*)out);
     return launched("argmax");
 }
 
