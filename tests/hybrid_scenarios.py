@@ -105,6 +105,25 @@ def other_sizes(make, tol):
         _check(got["a"], HC.oracle_logits(cfg, w, P["a"]), tol, f"sizes {k}")
 
 
+def wider_sizes(make, tol):
+    """Sizes past one warp's width: latents of 130 and 300, rotated parts of 72 (64 of them rotated) and 40, recurrent heads of 136 and
+    70 dimensions, nine heads (more than a block of the attention kernel takes), ten experts of which four, six taps."""
+    stacks = [
+        dict(layers=[dict(HC.latent(heads=9, dim=20, rot_dim=72, rot_dims=64, vdim=24, kv_rank=130, q_rank=50), mlp=HC.moe(experts=10, top=4, ff=40)),
+                     dict(HC.lightning(heads=2, dim=136, vdim=11, decay=(0.97, 0.8)), mlp=None)], width=96, groups=2, taps=6, vocab=77),
+        dict(layers=[dict(HC.lightning(heads=3, dim=70, vdim=33, decay=(0.999, 0.9, 0.6)), mlp=HC.moe(experts=2, top=1, ff=72)),
+                     dict(HC.latent(heads=2, dim=48, rot_dim=40, rot_dims=40, vdim=40, kv_rank=300, q_rank=33, scale=0.1), mlp=None)],
+             width=64, groups=4, taps=2, vocab=50),
+    ]
+    for k, kw in enumerate(stacks):
+        cfg = HC.config(**kw)
+        w = HC.random_tensors(cfg, seed=20 + k)
+        P = HC.prompts_for(cfg, {"a": 70, "b": 5})
+        got = HC.replay(make(cfg, w), P, [[("a", 60), ("b", 2)], [("a", 7), ("b", 1)], [("a", 1), ("b", 2)], [("a", 1)], [("a", 1)]])
+        for name in P:
+            _check(got[name], HC.oracle_logits(cfg, w, P[name]), tol, f"wider sizes {k} {name}")
+
+
 def greedy_generation(make, tol, new=10):
     """batched_generate (the scheduler's own admission, chunking and retirement, greedy sampling on the device) against the
     oracle generating greedily; a position whose two best oracle logits are closer than the tolerance may differ."""
@@ -127,4 +146,5 @@ def greedy_generation(make, tol, new=10):
             toks.append(t)
 
 
-ALL = [whole_prompt, prefill_then_decode, token_by_token, portions, unequal_batch, reuse_of_pages_and_slots, other_sizes, greedy_generation]
+ALL = [whole_prompt, prefill_then_decode, token_by_token, portions, unequal_batch, reuse_of_pages_and_slots, other_sizes, wider_sizes,
+       greedy_generation]
