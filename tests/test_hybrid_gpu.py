@@ -220,3 +220,83 @@ def test_decode_graph_replay_equals_eager_launches(monkeypatch):
         out[graphs] = [list(s.generated) for s in seqs]
         assert bool(eng._hybrid_graphs) == (graphs == "1")
     assert out["0"] == out["1"]
+
+
+def _write_checkpoint(folder, cfg, tensors):
+    """config.json + model.safetensors (bfloat16) as a Gulozen checkpoint is laid out."""
+    import json
+    from safetensors.torch import save_file
+    (folder / "config.json").write_text(json.dumps(cfg))
+    save_file({k: v.to(torch.bfloat16).contiguous() for k, v in tensors.items()}, str(folder / "model.safetensors"))
+
+
+def test_pipeline_serves_a_checkpoint_folder(tmp_path):
+    """pipeline(<folder>) picks the hybrid model class by config.json, loads the safetensors and generates what an engine built
+    from the same tensors generates; a checkpoint that lacks a tensor is refused by name."""
+    import lmdeploy_b200 as lmdeploy
+    from lmdeploy_b200.turbomind.engine import batched_generate
+    cfg = HC.config()
+    w = HC.random_tensors(cfg, seed=12)
+    _write_checkpoint(tmp_path, cfg, w)
+    P = HC.prompts_for(cfg, {"a": 9, "b": 70})
+    gen = lmdeploy.GenerationConfig(max_new_tokens=8, ignore_eos=True)
+    ecfg = lmdeploy.TurbomindEngineConfig(max_batch_size=2, session_len=256, cache_max_entry_count=8)
+    pipe = lmdeploy.pipeline(str(tmp_path), ecfg)
+    assert pipe.engine.hybrid and pipe.engine.spec.arch == "gulozen" and pipe.engine.spec.dtype == "bf16"
+    got = [r.token_ids for r in pipe([P["a"], P["b"]], gen)]
+    want = [list(s.generated) for s in batched_generate(HC.build_engine(cfg, w, device="cuda", dtype="bf16"), [P["a"], P["b"]], gen)]
+    assert got == want and all(len(x) == 8 for x in got)
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    _write_checkpoint(bad, cfg, {k: v for k, v in w.items() if k != "l1.mix.sink"})
+    with pytest.raises(KeyError, match="l1.mix.sink"):
+        lmdeploy.pipeline(str(bad), ecfg)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 6e-2)])
+def test_trace_runner_replays_a_schedule(tmp_path, dtype, tol):
+    """bin/trace_run as a process: three requests over a pool of three pages, portions beside single tokens, a request that sits a
+    step out, pages and slots given back at "end" and used again; the logits it writes against the oracle."""
+    import json
+    import os
+    import subprocess
+    import sys
+    cfg = HC.config()
+    w = HC.random_tensors(cfg, seed=13)
+    model, out = tmp_path / "model", tmp_path / "out"
+    model.mkdir()
+    _write_checkpoint(model, cfg, w)
+    P = HC.prompts_for(cfg, {"a": 100, "b": 6, "c": 64})
+    steps = [[("a", 62, [0, 61]), ("b", 2, [1])], [("a", 3, [0, 1, 2]), ("b", 1, [0])], [("b", 3, [2])], [("a", 35, [34]), ("c", 2, [])],
+             [("c", 62, [0, 61])], [("b2", 6, [5])]]
+    at, lines, asked = {}, [], []
+    for k, step in enumerate(steps):
+        entries, end = [], []
+        for name, count, want in step:
+            toks = P[name.rstrip("2")]
+            lo = at.get(name, 0)
+            at[name] = lo + count
+            entries.append({"id": name, "tokens": toks[lo:lo + count], "want": want})
+            asked += [(k, name.rstrip("2"), lo + x) for x in want]
+            if at[name] == len(toks):
+                end.append(name)
+        lines.append(json.dumps({"step": k, "entries": entries, "end": end}))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "192"], input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [x for x in r.stdout.split("\n") if x.startswith("done")] == [f"done {k}" for k in range(len(steps))]
+    oracle = {name: HC.oracle_logits(cfg, w, toks) for name, toks in P.items()}
+    rows = {}
+    for k in range(len(steps)):
+        want_here = [(n, p) for kk, n, p in asked if kk == k]
+        path = out / f"{k}.f32"
+        if not want_here:
+            assert not path.exists()
+            continue
+        got = np.fromfile(path, dtype="<f4").reshape(len(want_here), cfg["vocab"])
+        for (n, p), row in zip(want_here, got):
+            rows.setdefault(n, []).append((row, oracle[n][p]))
+    for n, pairs in rows.items():
+        err = HC.rel_error(np.stack([a for a, _ in pairs]), np.stack([b for _, b in pairs]))
+        assert (err.max() if tol < 1e-3 else np.median(err)) <= tol, (n, err)
