@@ -3,9 +3,8 @@
 // Replaces  invokeQkRMSNorm  (src/turbomind/kernels/norm/rms_norm.cu:139-260), called on the QKV GEMM output by
 //           UnifiedAttentionLayer (models/llama/unified_attention_layer.cc:739).
 //
-// The arithmetic follows the instruction sequence of the reference kernel as its release build compiles it
-// (`cuobjdump -sass` of oracle/_ref/libtm_ref_norm.so, QkRMSNorm<T, float, 8, 128>): 16 lanes own one head, 8 elements
-// each; sum of squares as an fp32 FMA chain over the lane's 8 elements in order, starting from 0; butterfly over lane
+// The arithmetic follows the order of operations of the reference kernel's source (QkRMSNorm<T, float, 8, 128>): 16 lanes
+// own one head, 8 elements each; sum of squares as an fp32 FMA chain over the lane's 8 elements in order, starting from 0; butterfly over lane
 // distances 8, 4, 2, 1; r = rsqrt.approx(fma(sum, 1/dim, eps)); y = T(float(x) * r) *_T w.  The same grouping here makes
 // the result bit-identical by construction, not by tolerance.
 #include "../../include/b200_turbomind.h"
