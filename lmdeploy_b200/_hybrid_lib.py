@@ -37,6 +37,20 @@ class ExpertArgs(C.Structure):
     ]
 
 
+class WindowArgs(C.Structure):
+    """b200h_window_args."""
+    _fields_ = [
+        ("n", C.c_int), ("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("block_len", C.c_int),
+        ("window", C.c_int), ("splits", C.c_int), ("scale", C.c_float), ("softcap", C.c_float), ("eps", C.c_float),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("ld", C.c_int64),
+        ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("qn", C.c_void_p),
+        ("r1", C.c_void_p), ("r2", C.c_void_p), ("talk", C.c_void_p), ("gate", C.c_void_p), ("ld_gate", C.c_int64),
+        ("ml", C.c_void_p), ("o_part", C.c_void_p), ("y", C.c_void_p),
+        ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("block_ptrs", C.c_void_p), ("cu_blocks", C.c_void_p),
+        ("layer_off", C.c_int64), ("v_off", C.c_int64), ("dtype", C.c_int), ("stream", C.c_void_p),
+    ]
+
+
 _lib = None
 P, I, L64, F = C.c_void_p, C.c_int, C.c_int64, C.c_float
 
@@ -68,6 +82,11 @@ def load():
     lib.b200h_silu_mul.argtypes = [P, P, P, L64, I, P]
     lib.b200h_weighted_scatter.argtypes = [P, P, P, P, I, I, I, P]
     lib.b200h_argmax.argtypes = [P, L64, I, I, P, P]
+    lib.b200h_add_rows.argtypes = [P, P, P, I, I, I, I, P]
+    lib.b200h_residual_norm.argtypes = [P, P, P, P, I, I, F, P, I, P]
+    lib.b200h_relu2.argtypes = [P, L64, I, P]
+    lib.b200h_window_prep.argtypes = [C.POINTER(WindowArgs)]
+    lib.b200h_window_attention.argtypes = [C.POINTER(WindowArgs)]
     _lib = lib
     return lib
 

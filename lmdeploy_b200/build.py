@@ -74,8 +74,9 @@ def build_hybrid(force=False):
     translation unit, independent of libb200tm.so so that serving such a model compiles nothing else).  Rebuilt when the
     source or its header is newer; concurrent builders write to a private name and rename."""
     hdr = os.path.join(REPO, "include", "b200_hybrid.h")
-    if not force and os.path.exists(HYBRID_LIB) and \
-            os.path.getmtime(HYBRID_LIB) >= max(os.path.getmtime(HYBRID_SRC), os.path.getmtime(hdr)):
+    hdir = os.path.dirname(HYBRID_SRC)
+    newest = max([os.path.getmtime(hdr)] + [os.path.getmtime(os.path.join(hdir, f)) for f in os.listdir(hdir) if f.endswith((".cu", ".cuh"))])
+    if not force and os.path.exists(HYBRID_LIB) and os.path.getmtime(HYBRID_LIB) >= newest:
         return HYBRID_LIB
     os.makedirs(LIBDIR, exist_ok=True)
     tmp = f"{HYBRID_LIB}.{os.getpid()}.tmp"

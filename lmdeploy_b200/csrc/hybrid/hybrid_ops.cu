@@ -673,6 +673,8 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int 
     }
 }
 
+#include "window_attention.cuh"
+
 }  // namespace b200h
 
 // ===================================================================================================== C ABI
@@ -965,3 +967,99 @@ B200H_API int b200h_argmax(const void* logits, int64_t ld, int rows, int vocab, 
     return launched("argmax");
 }
 
+
+// ------------------------------------------------------------------------------------------------ pre-norm blocks
+B200H_API int b200h_add_rows(void* x, const void* table, const void* idx, int fixed, int n, int width, int dtype, void* stream)
+{
+    if (!x || !table || n < 0 || width <= 0 || (!idx && fixed < 0)) return fail(B200H_ERR_INVALID_ARG, "add_rows: bad arguments");
+    if (n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, add_rows_kernel<T><<<n, 256, 0, st>>>((float*)x, (const T*)table, (const int*)idx, fixed, width));
+    return launched("add_rows");
+}
+
+B200H_API int b200h_residual_norm(void* x, const void* m, const void* extra, const void* w, int n, int width, float eps, void* h,
+                                  int dtype, void* stream)
+{
+    if (!x || n < 0 || width <= 0 || (h && !w)) return fail(B200H_ERR_INVALID_ARG, "residual_norm: bad arguments");
+    if (n == 0 || (!m && !extra && !h)) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, residual_norm_kernel<T><<<n, 256, 0, st>>>((float*)x, (const T*)m, (const T*)extra, (const float*)w, width, eps,
+                                                                      (float*)h));
+    return launched("residual_norm");
+}
+
+B200H_API int b200h_relu2(void* x, int64_t count, int dtype, void* stream)
+{
+    if (!x || count < 0) return fail(B200H_ERR_INVALID_ARG, "relu2: bad arguments");
+    if (count == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    B200H_DISPATCH_T(dtype, relu2_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, st>>>((T*)x, count));
+    return launched("relu2");
+}
+
+static int window_args_ok(const b200h_window_args* a, const char** why)
+{
+    if (!a || !a->tok_seq || !a->tok_pos || !a->block_ptrs || !a->cu_blocks || !a->qn) { *why = "window attention: bad arguments"; return 0; }
+    if (a->heads <= 0 || a->kv_heads <= 0 || a->heads % a->kv_heads || a->dim <= 0 || a->vdim <= 0 || a->block_len <= 0 || a->window < 0) {
+        *why = "window attention: heads must be a multiple of kv_heads, sizes positive";
+        return 0;
+    }
+    return 1;
+}
+
+B200H_API int b200h_window_prep(const b200h_window_args* a)
+{
+    const char* why = "";
+    if (!window_args_ok(a, &why)) return fail(B200H_ERR_INVALID_ARG, why);
+    if (!a->q || !a->k || !a->v) return fail(B200H_ERR_INVALID_ARG, "window_prep: bad arguments");
+    if (a->n == 0) return 0;
+    cudaStream_t st = (cudaStream_t)a->stream;
+    B200H_DISPATCH_T(a->dtype, window_prep_kernel<T><<<a->n, 256, 0, st>>>(
+        (const T*)a->q, (const T*)a->k, (const T*)a->v, a->ld, a->heads * a->dim, a->kv_heads * a->dim, a->kv_heads * a->vdim,
+        (const float*)a->q_norm, (const float*)a->k_norm, a->eps, (const int*)a->tok_seq, (const int*)a->tok_pos,
+        (const int64_t*)a->block_ptrs, (const int*)a->cu_blocks, a->layer_off, a->v_off, a->block_len, (float*)a->qn));
+    return launched("window_prep");
+}
+
+template <typename T, bool VEC>
+static int launch_window_attention(const b200h_window_args* a, const WindowGeom& g, cudaStream_t st)
+{
+    const int H = a->heads, rep = H / a->kv_heads;
+    const size_t stats_smem = (size_t)rep * a->dim * sizeof(float);
+    const size_t pv_smem = ((size_t)H * a->dim + 2 * H + (a->talk ? (size_t)H * H : 0) + (size_t)(a->talk ? 2 : 1) * H * kWinTile +
+                            (size_t)H * a->vdim) * sizeof(float);
+    if (stats_smem > 200 * 1024 || pv_smem > 200 * 1024)
+        return fail(B200H_ERR_UNSUPPORTED, "window_attention: heads * (dim + vdim + heads) floats exceed an SM's shared memory");
+    if (stats_smem > 48 * 1024)
+        cudaFuncSetAttribute(window_stats_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stats_smem);
+    if (pv_smem > 48 * 1024) cudaFuncSetAttribute(window_pv_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem);
+    window_stats_kernel<T, VEC><<<dim3(a->n, a->kv_heads, a->splits), 128, stats_smem, st>>>((const float*)a->qn, g, (float*)a->ml);
+    window_pv_kernel<T, VEC><<<dim3(a->n, a->splits), 256, pv_smem, st>>>((const float*)a->qn, g, (const float*)a->ml, (float*)a->o_part);
+    window_out_kernel<T><<<a->n, 256, 0, st>>>((const float*)a->o_part, a->splits, H * a->vdim, (const T*)a->gate, a->ld_gate, (T*)a->y);
+    return 0;
+}
+
+B200H_API int b200h_window_attention(const b200h_window_args* a)
+{
+    const char* why = "";
+    if (!window_args_ok(a, &why)) return fail(B200H_ERR_INVALID_ARG, why);
+    if (!a->ml || !a->o_part || !a->y || a->splits < 1 || a->splits > 65535 || a->kv_heads > 65535 || (a->r1 && !a->r2))
+        return fail(B200H_ERR_INVALID_ARG, "window_attention: bad arguments");
+    if (a->n == 0) return 0;
+    WindowGeom g;
+    g.heads = a->heads; g.kv_heads = a->kv_heads; g.dim = a->dim; g.vdim = a->vdim; g.block_len = a->block_len;
+    g.window = a->window; g.splits = a->splits; g.scale = a->scale; g.softcap = a->softcap;
+    g.r1 = (const float*)a->r1; g.r2 = (const float*)a->r2; g.talk = (const float*)a->talk;
+    g.tok_seq = (const int*)a->tok_seq; g.tok_pos = (const int*)a->tok_pos;
+    g.block_ptrs = (const int64_t*)a->block_ptrs; g.cu_blocks = (const int*)a->cu_blocks;
+    g.layer_off = a->layer_off; g.v_off = a->v_off;
+    cudaStream_t st = (cudaStream_t)a->stream;
+    const size_t esize = a->dtype == B200H_F32 ? 4 : 2;
+    const bool vec = (a->dim * esize) % 16 == 0 && a->layer_off % 16 == 0;
+    int rc = 0;
+    if (vec) { B200H_DISPATCH_T(a->dtype, rc = launch_window_attention<T, true>(a, g, st)); }
+    else { B200H_DISPATCH_T(a->dtype, rc = launch_window_attention<T, false>(a, g, st)); }
+    if (rc) return rc;
+    return launched("window_attention");
+}

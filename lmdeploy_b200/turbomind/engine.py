@@ -137,6 +137,8 @@ class TurboMind:
         if cfg.enable_prefix_caching:
             raise NotImplementedError("prefix caching with recurrent state (the state at a block border is not kept)")
         self.session_len = cfg.session_len or spec.session_len or 2048
+        if spec.max_positions:                      # learned positions: nothing is fed past the table (the token after it may be sampled)
+            self.session_len = min(self.session_len, spec.max_positions + 1)
         self.block_len = cfg.cache_block_seq_len
         self.model = model or HybridModel(spec, block_len=self.block_len, max_batch=self.max_batch)
         if model is None:

@@ -2,9 +2,13 @@
 
 A hybrid decoder mixes layer kinds, so a sequence owns two things between steps:
   * pages of the engine's block pool (runtime.KvCachePool, handed out by scheduler.BlockAllocator) -- every latent-attention
-    layer keeps, per position, its normed key/value latent (as T) and the rotated key part all heads share (as float);
+    layer keeps, per position, its normed key/value latent (as T) and the rotated key part all heads share (as float); every
+    windowed-attention layer its normed keys and its values (as T);
   * one slot of the StatePool (handed out by scheduler.Scheduler's slot list) -- per layer the last taps-1 inputs of the
-    short convolution, and per decayed-linear-attention layer the [heads, vdim, dim] float state.
+    short convolution (of both sublayers in pre-norm blocks), and per decayed-linear-attention layer the [heads, vdim, dim]
+    float state.
+A layer that a spec loops (HybridSpec.loop) is executed several times per step with the same weights: caches and states
+belong to RUNS (HybridSpec.runs()), weights to layers.
 The step is a mixed step like b200_model_chunk_step: any number of rows per sequence, prompt portions beside single decoded
 tokens; kernels address rows through (sequence, position) arrays, pages through the block table, state through the slot.
 
@@ -71,26 +75,39 @@ class HybridModel:
         self.T, self.dt = _TORCH_T[spec.dtype], _DT[spec.dtype]
         self.block_len, self.max_batch = block_len, max_batch
         esize = 2 if spec.dtype == "bf16" else 4
-        # cache page: the latent layers' regions one after another; in a region [block_len, kv_rank] T then [block_len, rot_dim] float
-        # state slot: per layer [taps-1, width] conv inputs, then per decay layer [heads, vdim, dim]
-        self.cache_off, self.rot_off, self.conv_off, self.mix_off = {}, {}, {}, {}
+        # cache page: the attention runs' regions one after another; a latent region is [block_len, kv_rank] T then [block_len, rot_dim] float
+        # state slot: per run [taps-1, width] conv inputs (twice where the feed-forward has a conv too), then per decay layer [heads, vdim, dim]
+        self.cache_off, self.rot_off, self.conv_off, self.mix_off, self.conv2_off, self.v_off = {}, {}, {}, {}, {}, {}
+        self.runs = spec.runs()
+        if spec.block not in ("post_norm", "pre_norm"):
+            raise NotImplementedError(f"block {spec.block!r}")
+        pre = spec.block == "pre_norm"
         page = slot = 0
         taps = spec.conv_taps
-        for i, layer in enumerate(spec.layers):
+        for r, (i, _) in enumerate(self.runs):
+            layer = spec.layers[i]
             m = layer.mixer
-            self.conv_off[i] = slot
+            self.conv_off[r] = slot
             slot += (taps - 1) * spec.width
+            if pre and layer.mlp is not None:
+                self.conv2_off[r] = slot
+                slot += (taps - 1) * spec.width
             if m.kind == "latent_attention":
                 if m.kv_rank > 512 or m.rot_dim > 128:
                     raise NotImplementedError("latent attention: kv_rank <= 512 and rot_dim <= 128")
-                self.cache_off[i] = page
-                self.rot_off[i] = _align(block_len * m.kv_rank * esize)
-                page += self.rot_off[i] + _align(block_len * m.rot_dim * 4)
+                self.cache_off[r] = page
+                self.rot_off[r] = _align(block_len * m.kv_rank * esize)
+                page += self.rot_off[r] + _align(block_len * m.rot_dim * 4)
             elif m.kind == "lightning":
                 if m.dim > 256:
                     raise NotImplementedError("decayed linear attention: dim <= 256")
-                self.mix_off[i] = slot
+                self.mix_off[r] = slot
                 slot += m.heads * m.vdim * m.dim
+            elif m.kind == "window_attention":
+                # in a region [block_len, kv_heads * dim] keys as T then [block_len, kv_heads * vdim] values as T
+                self.cache_off[r] = page
+                self.v_off[r] = _align(block_len * m.kv_heads * m.dim * esize)
+                page += self.v_off[r] + _align(block_len * m.kv_heads * m.vdim * esize)
             else:
                 raise NotImplementedError(m.kind)
         self.block_bytes = max(page, 16)
@@ -138,14 +155,26 @@ class HybridModel:
             return t.to(dev).contiguous()
 
         W = s.width
+        pre = s.block == "pre_norm"
+
+        def norm_w(name):
+            # pre-norm blocks store a norm weight as its deviation from one: the kernels get the full factor
+            t = f32(name, (W,))
+            return t + 1.0 if pre else t
+
         w["embed"] = lin("embed", shape=(s.vocab, W))
         w["head"] = lin("head", shape=(s.vocab, W))
-        w["final.norm"] = f32("final.norm", (W,))
+        w["final.norm"] = norm_w("final.norm")
+        if s.max_positions:
+            w["pos"] = lin("pos", shape=(s.max_positions, W))
+        if s.loop is not None:
+            w["loop.step"] = lin("loop.step", shape=(s.loop[2], W))
         for i, layer in enumerate(s.layers):
             p, m = f"l{i}.", layer.mixer
-            w[p + "norm1"] = f32(p + "norm1", (W,))
+            w[p + "norm1"] = norm_w(p + "norm1")
             w[p + "canon1"] = f32(p + "canon1", (W, s.conv_taps))
-            w[p + "dwa"] = f32(p + "dwa", (i + 2,))
+            if not pre:
+                w[p + "dwa"] = f32(p + "dwa", (i + 2,))
             if m.kind == "latent_attention":
                 HV = m.heads * m.vdim
                 w[p + "in"] = lin(p + "mix.dq", p + "mix.dkv", p + "mix.g", shape=(m.q_rank + m.kv_rank + m.rot_dim + HV, W))
@@ -159,6 +188,24 @@ class HybridModel:
                 freqs, mag = m.rot.frequencies()
                 w[p + "freqs"] = torch.tensor(freqs, dtype=torch.float64, device=dev)
                 w[p + "mag"] = float(mag)
+            elif m.kind == "window_attention":
+                HD, GD, GV, HV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
+                parts = [p + "mix.q", p + "mix.k", p + "mix.v"] + ([p + "mix.g"] if m.gate else [])
+                w[p + "in"] = lin(*parts, shape=(HD + GD + GV + (HV if m.gate else 0), W))
+                if m.bias:
+                    b = torch.cat([get(p + f"mix.{k}.b").to(torch.float32) for k in "qkv"] + ([torch.zeros(HV)] if m.gate else []))
+                    if b.numel() != w[p + "in"].shape[0]:
+                        raise ValueError(f"{p}mix.[qkv].b: {b.numel()} entries, expected {HD + GD + GV}")
+                    w[p + "in.b"] = b.to(dev, T).contiguous()
+                w[p + "o"] = lin(p + "mix.o", shape=(W, HV))
+                if m.qk_norm:
+                    w[p + "q.norm"] = f32(p + "mix.q.norm", (HD,))
+                    w[p + "k.norm"] = f32(p + "mix.k.norm", (GD,))
+                if m.distance_bias:
+                    w[p + "r1"] = f32(p + "mix.r1", (m.heads,))
+                    w[p + "r2"] = f32(p + "mix.r2", (m.heads,))
+                if m.talking_heads:
+                    w[p + "talk"] = f32(p + "mix.talk", (m.heads, m.heads))
             else:
                 HD, HV = m.heads * m.dim, m.heads * m.vdim
                 w[p + "in"] = lin(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g", shape=(2 * HD + 2 * HV, W))
@@ -167,7 +214,13 @@ class HybridModel:
                 w[p + "decay"] = torch.tensor(m.decay, dtype=torch.float32, device=dev)
             f = layer.mlp
             if f is not None:
-                w[p + "norm2"] = f32(p + "norm2", (W,))
+                w[p + "norm2"] = norm_w(p + "norm2")
+                if pre:
+                    w[p + "canon2"] = f32(p + "canon2", (W, s.conv_taps))
+                if f.kind == "dense":
+                    w[p + "up"] = lin(p + "mlp.up", shape=(f.ff, W))
+                    w[p + "down"] = lin(p + "mlp.down", shape=(W, f.ff))
+                    continue
                 w[p + "router"] = f32(p + "mlp.router", (f.experts, W))
                 for part, shape in (("gate", (f.ff, W)), ("up", (f.ff, W)), ("down", (W, f.ff))):
                     w[p + part] = torch.stack([lin(f"{p}mlp.e{e}.{part}", shape=shape) for e in range(f.experts)]).contiguous()
@@ -181,10 +234,18 @@ class HybridModel:
 
         def get(name):
             shape = self.tensor_shapes()[name]
+            if name.endswith(("norm1", "norm2", "final.norm")) and self.spec.block == "pre_norm":
+                return 0.1 * torch.randn(shape, generator=g)            # stored as the deviation from one
             if name.endswith(("norm1", "norm2", ".norm")):
                 return 1.0 + 0.1 * torch.randn(shape, generator=g)
-            if name.endswith("canon1"):
+            if name.endswith(("canon1", "canon2")):
                 return torch.randn(shape, generator=g) / taps
+            if name.endswith((".r1", ".r2")):
+                return torch.rand(shape, generator=g)
+            if name.endswith(".talk"):
+                return torch.eye(shape[0]) + 0.1 * torch.randn(shape, generator=g)
+            if name.endswith(".b") or name in ("pos", "loop.step"):
+                return (0.1 * torch.randn(shape, generator=g)).to(torch.bfloat16)
             if name.endswith("dwa"):
                 return torch.softmax(torch.randn(shape, generator=g), 0)
             if name.endswith("sink"):
@@ -197,23 +258,49 @@ class HybridModel:
     def tensor_shapes(self):
         """Checkpoint tensor names -> shapes for this spec."""
         s, W = self.spec, self.spec.width
+        pre = s.block == "pre_norm"
         out = {"embed": (s.vocab, W), "head": (s.vocab, W), "final.norm": (W,)}
+        if s.max_positions:
+            out["pos"] = (s.max_positions, W)
+        if s.loop is not None:
+            out["loop.step"] = (s.loop[2], W)
         for i, layer in enumerate(s.layers):
             p, m = f"l{i}.", layer.mixer
-            out.update({p + "norm1": (W,), p + "canon1": (W, s.conv_taps), p + "dwa": (i + 2,)})
+            out.update({p + "norm1": (W,), p + "canon1": (W, s.conv_taps)})
+            if not pre:
+                out[p + "dwa"] = (i + 2,)
             if m.kind == "latent_attention":
                 HV = m.heads * m.vdim
                 out.update({p + "mix.dq": (m.q_rank, W), p + "mix.dq.norm": (m.q_rank,), p + "mix.uq": (m.heads * (m.dim + m.rot_dim), m.q_rank),
                             p + "mix.dkv": (m.kv_rank + m.rot_dim, W), p + "mix.dkv.norm": (m.kv_rank,),
                             p + "mix.uk": (m.heads * m.dim, m.kv_rank), p + "mix.uv": (HV, m.kv_rank), p + "mix.sink": (m.heads,),
                             p + "mix.g": (HV, W), p + "mix.o": (W, HV)})
+            elif m.kind == "window_attention":
+                HD, GD, GV, HV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
+                out.update({p + "mix.q": (HD, W), p + "mix.k": (GD, W), p + "mix.v": (GV, W), p + "mix.o": (W, HV)})
+                if m.bias:
+                    out.update({p + "mix.q.b": (HD,), p + "mix.k.b": (GD,), p + "mix.v.b": (GV,)})
+                if m.qk_norm:
+                    out.update({p + "mix.q.norm": (HD,), p + "mix.k.norm": (GD,)})
+                if m.distance_bias:
+                    out.update({p + "mix.r1": (m.heads,), p + "mix.r2": (m.heads,)})
+                if m.talking_heads:
+                    out[p + "mix.talk"] = (m.heads, m.heads)
+                if m.gate:
+                    out[p + "mix.g"] = (HV, W)
             else:
                 HD, HV = m.heads * m.dim, m.heads * m.vdim
                 out.update({p + "mix.q": (HD, W), p + "mix.k": (HD, W), p + "mix.v": (HV, W), p + "mix.g": (HV, W),
                             p + "mix.o": (W, HV), p + "mix.norm": (HV,)})
             f = layer.mlp
             if f is not None:
-                out.update({p + "norm2": (W,), p + "mlp.router": (f.experts, W)})
+                out[p + "norm2"] = (W,)
+                if pre:
+                    out[p + "canon2"] = (W, s.conv_taps)
+                if f.kind == "dense":
+                    out.update({p + "mlp.up": (f.ff, W), p + "mlp.down": (W, f.ff)})
+                    continue
+                out[p + "mlp.router"] = (f.experts, W)
                 for e in range(f.experts):
                     out.update({f"{p}mlp.e{e}.gate": (f.ff, W), f"{p}mlp.e{e}.up": (f.ff, W), f"{p}mlp.e{e}.down": (W, f.ff)})
         return out
@@ -255,6 +342,12 @@ class HybridModel:
         s, lib, w, dev, T, dt = self.spec, self.lib, self.w, self.device, self.T, self.dt
         W, eps, groups = s.width, s.norm_eps, s.norm_groups
         st = self._stream()
+        if s.max_positions and max_pos >= s.max_positions:
+            raise ValueError(f"position {max_pos}: the model has {s.max_positions} learned positions")
+        if s.block == "pre_norm":
+            return self._step_pre_norm(n=n, batch=batch, tokens=tokens, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot,
+                                       block_ptrs=block_ptrs, cu_blocks=cu_blocks, state=state, rows=rows, n_rows=n_rows, max_pos=max_pos,
+                                       trace=trace)
         c = StepArrays(n=n, batch=batch, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot, block_ptrs=block_ptrs,
                        cu_blocks=cu_blocks, state=state, max_pos=max_pos)
         f32 = dict(dtype=torch.float32, device=dev)
@@ -267,7 +360,7 @@ class HybridModel:
         for i, layer in enumerate(s.layers):
             p = f"l{i}."
             h = self.conv_input(i, x, c)
-            y = self.latent_mixer(i, h, c) if layer.mixer.kind == "latent_attention" else self.decay_mixer(i, h, c)
+            y = self.mixer(i, i, h, c)
             with self.timed("gemm out"):
                 mixed = self._linear(y, w[p + "o"])
             f = layer.mlp
@@ -275,6 +368,8 @@ class HybridModel:
                 H.check(lib.b200h_residual_group_norm(x.data_ptr(), mixed.data_ptr(), 0, 1, w[p + "norm1"].data_ptr(), n, W, groups, eps,
                                                       xt.data_ptr() if f is not None else None, dt, st), "residual_group_norm")
             if f is not None:
+                if f.kind != "moe":
+                    raise NotImplementedError(f"post-norm blocks with a {f.kind!r} feed-forward")
                 out = self.routed_experts(i, x, xt, n)
                 with self.timed("residual + grouped norm"):
                     H.check(lib.b200h_residual_group_norm(x.data_ptr(), out.data_ptr(), 1, f.top, w[p + "norm2"].data_ptr(), n, W, groups,
@@ -288,6 +383,129 @@ class HybridModel:
             H.check(lib.b200h_group_norm_rows(x.data_ptr(), rows.data_ptr(), w["final.norm"].data_ptr(), n_rows, W, groups, eps,
                                               xn.data_ptr(), dt, st), "group_norm_rows")
             return self._logits(xn)
+
+    def _step_pre_norm(self, *, n, batch, tokens, tok_seq, tok_pos, cu_q, seq_slot, block_ptrs, cu_blocks, state, rows, n_rows, max_pos,
+                       trace=None):
+        """The step of pre-norm blocks: x <- x + mixer(conv(norm1(x))), x <- x + ff(conv(norm2(x))) per run.  A sublayer's output
+        joins the float stream inside the kernel that norms the stream for the next reader (residual add + norm in one pass)."""
+        s, lib, w, dev, T, dt = self.spec, self.lib, self.w, self.device, self.T, self.dt
+        W, eps, st = s.width, s.norm_eps, self._stream()
+        c = StepArrays(n=n, batch=batch, tok_seq=tok_seq, tok_pos=tok_pos, cu_q=cu_q, seq_slot=seq_slot, block_ptrs=block_ptrs,
+                       cu_blocks=cu_blocks, state=state, max_pos=max_pos)
+        x = torch.empty(n, W, dtype=torch.float32, device=dev)
+        with self.timed("embed"):
+            H.check(lib.b200h_embed(tokens.data_ptr(), w["embed"].data_ptr(), s.embedding_scale, x.data_ptr(), n, W, dt, st), "embed")
+            if s.max_positions:
+                H.check(lib.b200h_add_rows(x.data_ptr(), w["pos"].data_ptr(), tok_pos.data_ptr(), 0, n, W, dt, st), "add_rows")
+        pending = None                   # a sublayer's output (T) that the stream has not taken in yet
+        for r, (i, t) in enumerate(self.runs):
+            p, layer = f"l{i}.", s.layers[i]
+            extra = None
+            if t is not None and i == s.loop[0]:
+                extra = w["loop.step"].data_ptr() + t * W * w["loop.step"].element_size()
+            h = self.norm_conv_input(r, i, 1, x, pending, extra, c)
+            y = self.mixer(r, i, h, c)
+            with self.timed("gemm out"):
+                pending = self._linear(y, w[p + "o"])
+            f = layer.mlp
+            if f is not None:
+                h = self.norm_conv_input(r, i, 2, x, pending, None, c)
+                pending = self.dense_mlp(i, h)
+            if trace is not None:
+                H.check(lib.b200h_residual_norm(x.data_ptr(), pending.data_ptr(), None, None, n, W, eps, None, dt, st), "residual_norm")
+                pending = None
+                trace.append(x.clone())
+        xn = torch.empty(n_rows, W, dtype=T, device=dev)
+        with self.timed("final norm + head"):
+            if pending is not None:
+                H.check(lib.b200h_residual_norm(x.data_ptr(), pending.data_ptr(), None, None, n, W, eps, None, dt, st), "residual_norm")
+            H.check(lib.b200h_group_norm_rows(x.data_ptr(), rows.data_ptr(), w["final.norm"].data_ptr(), n_rows, W, 1, eps, xn.data_ptr(),
+                                              dt, st), "group_norm_rows")
+            return self._logits(xn)
+
+    def norm_conv_input(self, r, i, sub, x, pending, extra, c):
+        """What sublayer `sub` (1: mixer, 2: feed-forward) of run r reads: first the stream takes in `pending` (the previous
+        sublayer's output) and `extra` (a vector for all rows), then h = norm(x), then h + causal convolution of h over the
+        sequence (as T); advances the sublayer's conv state."""
+        s, w, n = self.spec, self.w, c.n
+        hn = torch.empty(n, s.width, dtype=torch.float32, device=self.device)
+        with self.timed("residual + norm"):
+            H.check(self.lib.b200h_residual_norm(x.data_ptr(), None if pending is None else pending.data_ptr(), extra,
+                                                 w[f"l{i}.norm{sub}"].data_ptr(), n, s.width, s.norm_eps, hn.data_ptr(), self.dt,
+                                                 self._stream()), "residual_norm")
+        return self.conv_input(i, hn, c, run=r, sub=sub)
+
+    def mixer(self, r, i, h, c):
+        """The sequence mixer of layer i in run r over its input h [n, width] (T) -> the output projection's input."""
+        kind = self.spec.layers[i].mixer.kind
+        if kind == "latent_attention":
+            return self.latent_mixer(i, h, c, run=r)
+        if kind == "window_attention":
+            return self.window_mixer(i, h, c, run=r)
+        return self.decay_mixer(i, h, c, run=r)
+
+    def window_splits(self, n, window, max_pos):
+        """Key ranges per row of a windowed-attention launch: one for prompt portions; a step of few rows cuts its window into
+        ranges of at least 32 keys until the launch has about two blocks per SM.  A power of two (the engine keys its decode
+        graphs on it)."""
+        keys = min(window, max_pos + 1) if window else max_pos + 1
+        want = min(296 // max(n, 1), keys // 32, 64)
+        splits = 1
+        while splits * 2 <= want:
+            splits *= 2
+        return splits
+
+    def window_mixer(self, i, h, c, run=None):
+        """Windowed attention of layer i: one stacked projection (q | k | v | gate) with its bias, RMS norm of q and k over their
+        whole projections + cache store, then attention over the window of cached keys with capped scores, distance penalty,
+        recombination of the heads' softmax weights, and the output gate.  Returns [n, heads * vdim] (T)."""
+        r = i if run is None else run
+        m, w, lib, dev, T, n = self.spec.layers[i].mixer, self.w, self.lib, self.device, self.T, c.n
+        p = f"l{i}."
+        HD, GD, GV, HV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
+        with self.timed("gemm in"):
+            proj = torch.addmm(w[p + "in.b"], h, w[p + "in"].t()) if m.bias else self._linear(h, w[p + "in"])
+        ld, es, base = proj.stride(0), proj.element_size(), proj.data_ptr()
+        f32 = dict(dtype=torch.float32, device=dev)
+        a = H.WindowArgs()
+        a.n, a.heads, a.kv_heads, a.dim, a.vdim, a.block_len, a.window = n, m.heads, m.kv_heads, m.dim, m.vdim, self.block_len, m.window
+        a.splits = self.window_splits(n, m.window, c.max_pos)
+        a.scale, a.softcap, a.eps = m.scale, m.softcap, self.spec.norm_eps
+        a.q, a.k, a.v, a.ld = base, base + es * HD, base + es * (HD + GD), ld
+        if m.qk_norm:
+            a.q_norm, a.k_norm = w[p + "q.norm"].data_ptr(), w[p + "k.norm"].data_ptr()
+        qn = torch.empty(n, HD, **f32)
+        a.qn = qn.data_ptr()
+        if m.distance_bias:
+            a.r1, a.r2 = w[p + "r1"].data_ptr(), w[p + "r2"].data_ptr()
+        if m.talking_heads:
+            a.talk = w[p + "talk"].data_ptr()
+        if m.gate:
+            a.gate, a.ld_gate = base + es * (HD + GD + GV), ld
+        ml = torch.empty(n, m.heads, a.splits, 2, **f32)
+        o_part = torch.empty(n, a.splits, HV, **f32)
+        y = torch.empty(n, HV, dtype=T, device=dev)
+        a.ml, a.o_part, a.y = ml.data_ptr(), o_part.data_ptr(), y.data_ptr()
+        a.tok_seq, a.tok_pos = c.tok_seq.data_ptr(), c.tok_pos.data_ptr()
+        a.block_ptrs, a.cu_blocks = c.block_ptrs.data_ptr(), c.cu_blocks.data_ptr()
+        a.layer_off, a.v_off, a.dtype, a.stream = self.cache_off[r], self.v_off[r], self.dt, self._stream()
+        with self.timed("qk norm + cache store"):
+            H.check(lib.b200h_window_prep(C.byref(a)), "window_prep")
+        with self.timed("windowed attention"):
+            H.check(lib.b200h_window_attention(C.byref(a)), "window_attention")
+        return y
+
+    def dense_mlp(self, i, h):
+        """Dense feed-forward of layer i over its input h [n, width] (T): down(act(up h)) -> [n, width] (T)."""
+        f, w = self.spec.layers[i].mlp, self.w
+        if f.act != "relu2":
+            raise NotImplementedError(f"activation {f.act!r}")
+        with self.timed("gemm up"):
+            a = self._linear(h, w[f"l{i}.up"])
+        with self.timed("squared relu"):
+            H.check(self.lib.b200h_relu2(a.data_ptr(), a.numel(), self.dt, self._stream()), "relu2")
+        with self.timed("gemm down"):
+            return self._linear(a, w[f"l{i}.down"])
 
     def _logits(self, xn):
         """Float logits of normed rows: bf16 operands keep a float result (no rounding of the logits to bf16)."""
@@ -311,19 +529,28 @@ class HybridModel:
 
     def decode_key(self, n, max_pos):
         """What a captured decode step depends on besides its row count."""
-        return tuple(self.attention_splits(n, l.mixer.heads, max_pos) for l in self.spec.layers if l.mixer.kind == "latent_attention")
+        key = []
+        for l in self.spec.layers:
+            if l.mixer.kind == "latent_attention":
+                key.append(self.attention_splits(n, l.mixer.heads, max_pos))
+            elif l.mixer.kind == "window_attention":
+                key.append(self.window_splits(n, l.mixer.window, max_pos))
+        return tuple(key)
 
-    def conv_input(self, i, x, c):
-        """What layer i's mixer reads: x + causal convolution of x over the sequence (as T); advances the layer's conv state."""
+    def conv_input(self, i, x, c, run=None, sub=1):
+        """What a sublayer of layer i reads (sub 1: the mixer, 2: the feed-forward): x + causal convolution of x over the sequence
+        (as T); advances that sublayer's conv state of the run."""
         s, w = self.spec, self.w
+        r = i if run is None else run
+        off = self.conv_off[r] if sub == 1 else self.conv2_off[r]
         h = torch.empty(c.n, s.width, dtype=self.T, device=self.device)
         with self.timed("causal conv"):
-            H.check(self.lib.b200h_causal_conv(x.data_ptr(), w[f"l{i}.canon1"].data_ptr(), c.state.ptr(self.conv_off[i]),
+            H.check(self.lib.b200h_causal_conv(x.data_ptr(), w[f"l{i}.canon{sub}"].data_ptr(), c.state.ptr(off),
                                                c.state.storage.stride(0), c.tok_seq.data_ptr(), c.cu_q.data_ptr(), c.seq_slot.data_ptr(),
                                                h.data_ptr(), c.n, c.batch, s.width, s.conv_taps, self.dt, self._stream()), "causal_conv")
         return h
 
-    def latent_mixer(self, i, h, c):
+    def latent_mixer(self, i, h, c, run=None):
         """Latent attention of layer i over rows h [n, width] (T): one stacked projection (query latent | key/value latent +
         shared rotated key | gate), norms + rotation + cache store, query expansion, attention over the paged latents with the
         sink, value expansion and gate.  Returns the gated heads [n, heads * vdim] (T), the output projection's input."""
@@ -345,7 +572,8 @@ class HybridModel:
         a.cq = cq.data_ptr()
         a.tok_seq, a.tok_pos = c.tok_seq.data_ptr(), c.tok_pos.data_ptr()
         a.block_ptrs, a.cu_blocks = c.block_ptrs.data_ptr(), c.cu_blocks.data_ptr()
-        a.layer_off, a.rot_off, a.dtype, a.stream = self.cache_off[i], self.rot_off[i], self.dt, self._stream()
+        r = i if run is None else run
+        a.layer_off, a.rot_off, a.dtype, a.stream = self.cache_off[r], self.rot_off[r], self.dt, self._stream()
         with self.timed("latent norm + rotate + cache store"):
             H.check(lib.b200h_latent_prep(C.byref(a)), "latent_prep")
         with self.timed("gemm query up"):
@@ -384,7 +612,7 @@ class HybridModel:
         except RuntimeError:
             return torch.bmm(a.float(), b.float())
 
-    def decay_mixer(self, i, h, c):
+    def decay_mixer(self, i, h, c, run=None):
         """Decayed linear attention of layer i: one stacked projection (q | k | v | gate), the per-head recurrence on the
         sequence's float state, then unit-rms norm over the concatenated heads times sigmoid(gate).  Returns [n, heads * vdim] (T)."""
         m, w, lib, dev, n = self.spec.layers[i].mixer, self.w, self.lib, self.device, c.n
@@ -397,7 +625,7 @@ class HybridModel:
         st = self._stream()
         with self.timed("decayed linear attention"):
             H.check(lib.b200h_decay_attention(base, base + es * HD, base + es * 2 * HD, ld, w[p + "decay"].data_ptr(),
-                                              c.state.ptr(self.mix_off[i]), c.state.storage.stride(0), c.cu_q.data_ptr(),
+                                              c.state.ptr(self.mix_off[i if run is None else run]), c.state.storage.stride(0), c.cu_q.data_ptr(),
                                               c.seq_slot.data_ptr(), c.batch, m.heads, m.dim, m.vdim, o.data_ptr(), self.dt, st),
                     "decay_attention")
         y = torch.empty(n, HV, dtype=self.T, device=dev)

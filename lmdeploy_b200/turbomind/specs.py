@@ -149,16 +149,47 @@ class DecayAttentionSpec:
 
 
 @dataclass(frozen=True)
+class WindowAttentionSpec:
+    """Softmax attention with grouped key/value heads over a sliding window of cached keys and values, without rotation.
+    Score of query i and key j (max(0, i - window + 1) <= j <= i): scale * q.k, capped as softcap * tanh(. / softcap), minus
+    r1_h * ln(1 + r2_h * (i - j)); after the softmax the heads' weight rows are recombined by a [heads, heads] matrix; the
+    concatenated heads are gated by sigmoid of a projection of the mixer's input.  The optional parts are switches, so that
+    another design can use the mechanism with some of them off."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int = 0               # visible positions, the query's own included; 0: all earlier positions
+    softcap: float = 0.0          # 0: scores are not capped
+    qk_norm: bool = True          # RMS norm of q and of k over the whole projection (all heads at once), plain weights
+    bias: bool = True             # q, k and v projections carry a bias
+    distance_bias: bool = True    # per-head r1, r2
+    talking_heads: bool = True    # [heads, heads] recombination of the softmax weights
+    gate: bool = True
+    kind = "window_attention"
+
+
+@dataclass(frozen=True)
 class RoutedExpertsSpec:
     experts: int
     top: int
     ff: int
+    kind = "moe"
+
+
+@dataclass(frozen=True)
+class DenseMlpSpec:
+    """down(act(up h)); act 'relu2' = the square of relu."""
+    ff: int
+    act: str = "relu2"
+    kind = "dense"
 
 
 @dataclass(frozen=True)
 class HybridLayerSpec:
-    mixer: object                       # LatentAttentionSpec | DecayAttentionSpec
-    mlp: RoutedExpertsSpec = None       # None: the layer has no feed-forward
+    mixer: object                       # LatentAttentionSpec | DecayAttentionSpec | WindowAttentionSpec
+    mlp: object = None                  # RoutedExpertsSpec | DenseMlpSpec | None: the layer has no feed-forward
 
 
 @dataclass(frozen=True)
@@ -174,11 +205,26 @@ class HybridSpec:
     embedding_scale: float
     dtype: str = "bf16"                 # 'bf16' | 'f32': the type of projections and their weights
     session_len: int = 0
+    # 'post_norm': conv -> mixer -> grouped RMS norm of the OUTPUT -> add, then the learned average over all earlier streams.
+    # 'pre_norm':  each sublayer reads conv(norm(x)) with an RMS norm whose stored weight is the deviation from one, and its
+    #              output is added to the stream as it is; the feed-forward has a conv of its own.
+    block: str = "post_norm"
+    max_positions: int = 0              # > 0: a learned vector per position is added to the embedding
+    loop: tuple = None                  # (start, stop, times): layers start..stop-1 run `times` times in a row with the same weights,
+    #                                     each pass with a cache and state of its own and a learned vector added before it
     hybrid = True
 
     @property
     def hidden(self):
         return self.width
+
+    def runs(self):
+        """[(layer index, pass index or None)] in execution order.  Caches and states belong to runs, weights to layers."""
+        L = len(self.layers)
+        if self.loop is None:
+            return [(i, None) for i in range(L)]
+        a, b, times = self.loop
+        return [(i, None) for i in range(a)] + [(i, t) for t in range(times) for i in range(a, b)] + [(i, None) for i in range(b, L)]
 
 
 def _gulozen_mixer(kind, m):
@@ -215,5 +261,36 @@ def gulozen_spec(cfg, name="gulozen"):
                       session_len=int(cfg.get("session_len", 0)))
 
 
+def bodopel_spec(cfg, name="bodopel"):
+    """config.json of a Bodopel checkpoint -> HybridSpec.  Every size and constant is read from the config."""
+    layers = []
+    for entry in cfg["layers"]:
+        if entry["type"] != "attention":
+            raise NotImplementedError(f"mixer type {entry['type']!r}")
+        m = entry["mixer"]
+        heads, kv_heads = int(m["heads"]), int(m["kv_heads"])
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads do not divide into {kv_heads} key/value heads")
+        mixer = WindowAttentionSpec(heads, kv_heads, int(m["dim"]), int(m["vdim"]), float(m["scale"]),
+                                    window=int((m.get("mask") or {}).get("size") or 0), softcap=float(m.get("softcap") or 0.0))
+        mlp = entry.get("mlp")
+        if mlp is not None:
+            if mlp.get("kind", "dense") != "dense":
+                raise NotImplementedError(f"feed-forward kind {mlp.get('kind')!r}")
+            mlp = DenseMlpSpec(int(mlp["ff"]))
+        layers.append(HybridLayerSpec(mixer, mlp))
+    loop = cfg.get("loop")
+    if loop is not None:
+        loop = (int(loop["start"]), int(loop["stop"]), int(loop["times"]))
+        if not 0 <= loop[0] <= loop[1] <= len(layers) or loop[2] < 1:
+            raise ValueError(f"loop {loop} over {len(layers)} layers")
+        if loop[0] == loop[1]:
+            loop = None
+    return HybridSpec(name=name, arch="bodopel", width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=tuple(layers),
+                      norm_eps=float(cfg["norm"]["eps"]), norm_groups=1, conv_taps=int(cfg["canon"]["taps"]),
+                      embedding_scale=float(cfg["embedding"]["scale"]), session_len=int(cfg["max_positions"]), block="pre_norm",
+                      max_positions=int(cfg["max_positions"]), loop=loop)
+
+
 # config.json "architecture" -> spec builder, for checkpoints that are not HF `architectures` configs
-HYBRID_ARCHITECTURES = {"Gulozen": gulozen_spec}
+HYBRID_ARCHITECTURES = {"Gulozen": gulozen_spec, "Bodopel": bodopel_spec}

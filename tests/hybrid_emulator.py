@@ -207,6 +207,83 @@ class EmulatedHybridLib:
         _f(out, rows, width)[to] = wt[to][:, None] * S_
         return 0
 
+    # ---- pre-norm blocks
+    def b200h_add_rows(self, x, table, idx, fixed, n, width, dtype, stream):
+        assert dtype == F32
+        X = _f(x, n, width)
+        which = _i(idx, n) if idx else np.full(n, fixed)
+        tab = _f(table, int(which.max()) + 1, width)
+        X += tab[which]
+        return 0
+
+    def b200h_residual_norm(self, x, m, extra, w, n, width, eps, h, dtype, stream):
+        X = _f(x, n, width)
+        if m:
+            X += _f(m, n, width)
+        if extra:
+            X += _f(extra, width)
+        if h:
+            _f(h, n, width)[:] = _unit(X, eps) * _f(w, width)
+        return 0
+
+    def b200h_relu2(self, x, count, dtype, stream):
+        X = _a(x, count)
+        X[:] = np.maximum(X, 0) ** 2
+        return 0
+
+    @staticmethod
+    def _kv(a, seq, pos):
+        """The cache entry of (seq, pos): key [kv_heads, dim] and value [kv_heads, vdim] views."""
+        cu = _i(a.cu_blocks, seq + 2)
+        ptrs = _a(a.block_ptrs, cu[seq + 1], C.c_int64)
+        base = int(ptrs[cu[seq] + pos // a.block_len]) + a.layer_off
+        at = pos % a.block_len
+        G, D, V = a.kv_heads, a.dim, a.vdim
+        return _f(base + 4 * at * G * D, G, D), _f(base + a.v_off + 4 * at * G * V, G, V)
+
+    def b200h_window_prep(self, args):
+        a = args._obj
+        assert a.dtype == F32
+        H, G, D, V = a.heads, a.kv_heads, a.dim, a.vdim
+        q, k, v = _rows(a.q, a.n, a.ld, H * D), _rows(a.k, a.n, a.ld, G * D), _rows(a.v, a.n, a.ld, G * V)
+        _f(a.qn, a.n, H * D)[:] = _unit(q, a.eps) * _f(a.q_norm, H * D) if a.q_norm else q
+        kn = _unit(k, a.eps) * _f(a.k_norm, G * D) if a.k_norm else k
+        seqs, poss = _i(a.tok_seq, a.n), _i(a.tok_pos, a.n)
+        for t in range(a.n):
+            kd, vd = self._kv(a, int(seqs[t]), int(poss[t]))
+            kd[:] = kn[t].reshape(G, D)
+            vd[:] = v[t].reshape(G, V)
+        return 0
+
+    def b200h_window_attention(self, args):
+        a = args._obj
+        H, G, D, V = a.heads, a.kv_heads, a.dim, a.vdim
+        rep = H // G
+        qn = _f(a.qn, a.n, H, D)
+        y = _f(a.y, a.n, H * V)
+        gate = _rows(a.gate, a.n, a.ld_gate, H * V) if a.gate else None
+        seqs, poss = _i(a.tok_seq, a.n), _i(a.tok_pos, a.n)
+        for t in range(a.n):
+            s, pos = int(seqs[t]), int(poss[t])
+            lo = max(0, pos - a.window + 1) if a.window > 0 else 0
+            ks, vs = zip(*[self._kv(a, s, j) for j in range(lo, pos + 1)])
+            ks, vs = np.stack(ks), np.stack(vs)                                    # [L, G, D], [L, G, V]
+            dist = (pos - np.arange(lo, pos + 1)).astype(np.float32)
+            wts = np.zeros((H, len(dist)), np.float32)
+            for h in range(H):
+                sc = (ks[:, h // rep] @ qn[t, h]) * np.float32(a.scale)
+                if a.softcap > 0:
+                    sc = a.softcap * np.tanh(sc / a.softcap)
+                if a.r1:
+                    sc = sc - _f(a.r1, H)[h] * np.log1p(_f(a.r2, H)[h] * dist)
+                e = np.exp(sc - sc.max())
+                wts[h] = e / e.sum()
+            if a.talk:
+                wts = _f(a.talk, H, H) @ wts
+            out = np.stack([wts[h] @ vs[:, h // rep] for h in range(H)]).reshape(H * V)
+            y[t] = out * _sigmoid(gate[t]) if gate is not None else out
+        return 0
+
     def b200h_argmax(self, logits, ld, rows, vocab, out, stream):
         _i(out, rows)[:] = _rows(logits, rows, ld, vocab).argmax(-1)
         return 0
