@@ -66,6 +66,18 @@ def hybrid_config(z):
             "layers": [{"type": t, "mixer": lat if t == "latent_attention" else lin, "mlp": mlp} for t in HYBRID_LAYERS]}
 
 
+def bodopel_bench_config(z, window=1024):
+    """A Bodopel config.json (dict) of size `z`: four windowed-attention layers with the dense decoder's head geometry (GQA, 128
+    dimensions per head, a window of 1024 keys) and a dense squared-relu feed-forward with the dense decoder's feed-forward
+    parameter count (two matrices of 1.5 * inter instead of three of inter)."""
+    d = z["dense"]
+    mixer = {"heads": d["heads"], "kv_heads": d["kv_heads"], "dim": 128, "vdim": 128, "mask": {"size": window}, "scale": 128 ** -0.5,
+             "softcap": 30.0}
+    return {"architecture": "Bodopel", "canon": {"taps": 4}, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "vocab": HYBRID_VOCAB,
+            "width": z["width"], "max_positions": 8192,
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": d["inter"] * 3 // 2}} for _ in HYBRID_LAYERS]}
+
+
 def _engine_throughput(torch, eng, vocab, batch, ctx, steps, warm):
     """Prompts of `ctx` tokens for `batch` requests through TurboMind.step: tokens/s of prompt ingestion (until every request
     has produced its first token) and of `steps` decode steps after `warm` untimed ones.  Wall clock around synchronised
@@ -106,16 +118,19 @@ def run_hybrid(args):
     from lmdeploy_b200.messages import TurbomindEngineConfig
     from lmdeploy_b200.turbomind import ModelSpec
     from lmdeploy_b200.turbomind.engine import TurboMind
-    from lmdeploy_b200.turbomind.specs import gulozen_spec
+    from lmdeploy_b200.turbomind.specs import bodopel_spec, gulozen_spec
     z = HYBRID_SIZES[args.hybrid]
     batch, ctx, steps, warm = args.hybrid_batch, args.hybrid_ctx, args.steps, max(args.warmup, 3)
     session = 2 * ctx + warm + steps + 16
     blocks = batch * ((session + 63) // 64) + 4
     out = {"metric": "hybrid_vs_dense_tokens_per_s", "size": args.hybrid, "batch": batch, "ctx": ctx, "steps": steps, "warmup": warm,
-           "dtype": "bf16 (hybrid) / f16 (dense)", "data": "synthetic", "layers": len(HYBRID_LAYERS)}
+           "dtype": "bf16 (hybrid) / f16 (dense)", "data": "synthetic", "layers": len(HYBRID_LAYERS), "design": args.hybrid_design}
     with ClockSampler() as clocks:
         clocks.wait_ready()
-        spec = gulozen_spec(hybrid_config(z), name=f"gulozen-{args.hybrid}")
+        if args.hybrid_design == "bodopel":
+            spec = bodopel_spec(bodopel_bench_config(z), name=f"bodopel-{args.hybrid}")
+        else:
+            spec = gulozen_spec(hybrid_config(z), name=f"gulozen-{args.hybrid}")
         eng = TurboMind(spec, TurbomindEngineConfig(dtype="bfloat16", max_batch_size=batch, session_len=session, cache_max_entry_count=blocks,
                                                     max_prefill_token_num=8192), seed=0)
         out["hybrid"], seqs = _engine_throughput(torch, eng, HYBRID_VOCAB, batch, ctx, steps, warm)
@@ -167,6 +182,9 @@ def parse():
     ap.add_argument("--hybrid", default=None, choices=list(HYBRID_SIZES),
                     help="instead of the default workload: prefill and decode tokens/s of a Gulozen hybrid decoder of this size "
                          "beside the dense decoder of equal size, both through the engine (random weights)")
+    ap.add_argument("--hybrid-design", default="gulozen", choices=["gulozen", "bodopel"],
+                    help="which hybrid design --hybrid builds: Gulozen (latent / decayed linear attention, routed experts) or Bodopel "
+                         "(windowed attention with grouped key/value heads, dense feed-forward)")
     ap.add_argument("--hybrid-batch", type=int, default=32)
     ap.add_argument("--hybrid-ctx", type=int, default=1024)
     ap.add_argument("--no-graph", action="store_true", help="do not capture the step in a CUDA graph")
