@@ -1022,20 +1022,39 @@ B200H_API int b200h_window_prep(const b200h_window_args* a)
     return launched("window_prep");
 }
 
-template <typename T, bool VEC>
-static int launch_window_attention(const b200h_window_args* a, const WindowGeom& g, cudaStream_t st)
+static size_t window_pv_smem(const b200h_window_args* a, int rows, int tile)
+{
+    const size_t H = a->heads, rh = (size_t)rows * H;
+    auto pad4 = [](size_t v) { return (v + 3) & ~(size_t)3; };
+    return (size_t)2 * tile * sizeof(char*) +
+           sizeof(float) * (pad4(rh * a->dim) + 2 * pad4(rh) + (a->talk ? pad4(H * H) : 0) + (size_t)(a->talk ? 2 : 1) * rh * tile + rh * a->vdim);
+}
+
+template <typename T, bool VEC, int CW>
+static int launch_window_attention(const b200h_window_args* a, WindowGeom g, cudaStream_t st)
 {
     const int H = a->heads, rep = H / a->kv_heads;
-    const size_t stats_smem = (size_t)rep * a->dim * sizeof(float);
-    const size_t pv_smem = ((size_t)H * a->dim + 2 * H + (a->talk ? (size_t)H * H : 0) + (size_t)(a->talk ? 2 : 1) * H * kWinTile +
-                            (size_t)H * a->vdim) * sizeof(float);
+    // Rows per block: four for prompt portions (one key range per row), one when the keys of a row are cut into ranges; keys per
+    // tile of pass 2: about one (key, key/value head) pair per thread.  Both shrink until a block fits half an SM's shared memory.
+    const size_t budget = 100 * 1024;
+    g.rows = (a->splits == 1 && a->n >= 4) ? 4 : 1;
+    g.tile = (256 / a->kv_heads) & ~3;
+    g.tile = g.tile < 32 ? 32 : (g.tile > 128 ? 128 : g.tile);
+    while (window_pv_smem(a, g.rows, g.tile) > budget && g.tile > 32) g.tile /= 2;
+    while (window_pv_smem(a, g.rows, g.tile) > budget && g.rows > 1) g.rows /= 2;
+    const size_t stats_smem = (size_t)g.rows * rep * a->dim * sizeof(float), pv_smem = window_pv_smem(a, g.rows, g.tile);
     if (stats_smem > 200 * 1024 || pv_smem > 200 * 1024)
         return fail(B200H_ERR_UNSUPPORTED, "window_attention: heads * (dim + vdim + heads) floats exceed an SM's shared memory");
     if (stats_smem > 48 * 1024)
         cudaFuncSetAttribute(window_stats_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stats_smem);
-    if (pv_smem > 48 * 1024) cudaFuncSetAttribute(window_pv_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem);
-    window_stats_kernel<T, VEC><<<dim3(a->n, a->kv_heads, a->splits), 128, stats_smem, st>>>((const float*)a->qn, g, (float*)a->ml);
-    window_pv_kernel<T, VEC><<<dim3(a->n, a->splits), 256, pv_smem, st>>>((const float*)a->qn, g, (const float*)a->ml, (float*)a->o_part);
+    if (pv_smem > 48 * 1024)
+        cudaFuncSetAttribute(window_pv_kernel<T, VEC, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem);
+    const int blocks = (a->n + g.rows - 1) / g.rows;
+    // pass 1: a thread per key of the range, at most 128
+    const int keys = a->window > 0 ? a->window + g.rows - 1 : 1 << 30, per = (keys + a->splits - 1) / a->splits;
+    const int stats_threads = per <= 32 ? 32 : (per <= 64 ? 64 : 128);
+    window_stats_kernel<T, VEC><<<dim3(blocks, a->kv_heads, a->splits), stats_threads, stats_smem, st>>>((const float*)a->qn, g, (float*)a->ml);
+    window_pv_kernel<T, VEC, CW><<<dim3(blocks, a->splits), 256, pv_smem, st>>>((const float*)a->qn, g, (const float*)a->ml, (float*)a->o_part);
     window_out_kernel<T><<<a->n, 256, 0, st>>>((const float*)a->o_part, a->splits, H * a->vdim, (const T*)a->gate, a->ld_gate, (T*)a->y);
     return 0;
 }
@@ -1048,6 +1067,7 @@ B200H_API int b200h_window_attention(const b200h_window_args* a)
         return fail(B200H_ERR_INVALID_ARG, "window_attention: bad arguments");
     if (a->n == 0) return 0;
     WindowGeom g;
+    g.n = a->n; g.rows = 1; g.tile = 32;
     g.heads = a->heads; g.kv_heads = a->kv_heads; g.dim = a->dim; g.vdim = a->vdim; g.block_len = a->block_len;
     g.window = a->window; g.splits = a->splits; g.scale = a->scale; g.softcap = a->softcap;
     g.r1 = (const float*)a->r1; g.r2 = (const float*)a->r2; g.talk = (const float*)a->talk;
@@ -1056,10 +1076,14 @@ B200H_API int b200h_window_attention(const b200h_window_args* a)
     g.layer_off = a->layer_off; g.v_off = a->v_off;
     cudaStream_t st = (cudaStream_t)a->stream;
     const size_t esize = a->dtype == B200H_F32 ? 4 : 2;
+    // 16-byte key reads / four value columns per read where sizes and offsets keep every read aligned
     const bool vec = (a->dim * esize) % 16 == 0 && a->layer_off % 16 == 0;
+    const bool vec_v = a->vdim % 4 == 0 && a->layer_off % 16 == 0 && a->v_off % 16 == 0;
     int rc = 0;
-    if (vec) { B200H_DISPATCH_T(a->dtype, rc = launch_window_attention<T, true>(a, g, st)); }
-    else { B200H_DISPATCH_T(a->dtype, rc = launch_window_attention<T, false>(a, g, st)); }
+    if (vec && vec_v) { B200H_DISPATCH_T(a->dtype, rc = (launch_window_attention<T, true, 4>(a, g, st))); }
+    else if (vec) { B200H_DISPATCH_T(a->dtype, rc = (launch_window_attention<T, true, 1>(a, g, st))); }
+    else if (vec_v) { B200H_DISPATCH_T(a->dtype, rc = (launch_window_attention<T, false, 4>(a, g, st))); }
+    else { B200H_DISPATCH_T(a->dtype, rc = (launch_window_attention<T, false, 1>(a, g, st))); }
     if (rc) return rc;
     return launched("window_attention");
 }

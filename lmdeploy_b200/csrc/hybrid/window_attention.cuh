@@ -8,17 +8,18 @@
 //
 // Attention runs in two passes over a row's visible keys [max(0, pos - window + 1), pos], both cut into `splits` equal key
 // ranges so that a step of few rows still fills the SMs:
-//   pass 1 (window_stats_kernel, one block per row, key/value head and range): scores of the heads that share the key/value
+//   pass 1 (window_stats_kernel, one block per row block, key/value head and range): scores of the heads that share the key/value
 //          head, their running maximum and denominator;
-//   pass 2 (window_pv_kernel, one block per row and range): the ranges' (maximum, denominator) pairs are merged per head, the
+//   pass 2 (window_pv_kernel, one block per row block and range): the ranges' (maximum, denominator) pairs are merged per head, the
 //          scores are computed again for ALL heads of the row, turned into final softmax weights, recombined across heads
 //          (weight'_h = sum_g talk[h, g] weight_g -- this couples every head of a row, hence one block for all of them) and
 //          applied to the values of each head's own key/value head;
 //   window_out_kernel sums the ranges' partial outputs, applies sigmoid(gate) and writes T.
+// A block takes `rows` consecutive rows of the step; those of one sequence (consecutive positions) walk their keys together, so a
+// cached key or value is read and converted once for all of them (prompt portions: 4 rows; a step of single tokens: 1).
 // Scores, softmax, recombination and the weighted value sums are float whatever T is.
 
 constexpr int kMaxRep = 8;              // query heads of one key/value head handled per walk over a key
-constexpr int kWinTile = 32;            // keys per tile of pass 2
 
 // x[t] += table[idx ? idx[t] : fixed]
 template <typename T>
@@ -99,7 +100,9 @@ __global__ void window_prep_kernel(const T* __restrict__ q, const T* __restrict_
 }
 
 struct WindowGeom {
-    int heads, kv_heads, dim, vdim, block_len, window, splits;
+    int n, heads, kv_heads, dim, vdim, block_len, window, splits;
+    int rows;                 // rows of the step per block (consecutive rows; a block walks the keys once for those of one sequence)
+    int tile;                 // keys per tile of pass 2, a multiple of 4, at most 256
     float scale, softcap;
     const float* r1;          // [heads] or nullptr: no distance penalty
     const float* r2;
@@ -111,13 +114,19 @@ struct WindowGeom {
     int64_t layer_off, v_off;
 };
 
-// The key range `z` of a row at position pos: [j0, j1).
-__device__ __forceinline__ void window_range(const WindowGeom& g, int pos, int z, int& j0, int& j1)
+// The key range `z` of consecutive rows of one sequence at positions first .. last: [j0, j1).  Every row masks the keys of the
+// range that it does not see.
+__device__ __forceinline__ void window_range(const WindowGeom& g, int first, int last, int z, int& j0, int& j1)
 {
-    const int lo = g.window > 0 ? max(0, pos - g.window + 1) : 0;
-    const int per = (pos - lo + g.splits) / g.splits;         // ceil((pos - lo + 1) / splits)
+    const int lo = g.window > 0 ? max(0, first - g.window + 1) : 0;
+    const int per = (last - lo + g.splits) / g.splits;         // ceil((last - lo + 1) / splits)
     j0 = lo + z * per;
-    j1 = min(pos + 1, j0 + per);
+    j1 = min(last + 1, j0 + per);
+}
+
+__device__ __forceinline__ bool window_sees(const WindowGeom& g, int pos, int j)
+{
+    return j <= pos && (g.window == 0 || j > pos - g.window);
 }
 
 // score of head `head` for a key at distance `dist` behind the query, from the raw dot product
@@ -129,7 +138,8 @@ __device__ __forceinline__ float window_score(const WindowGeom& g, float dot, in
     return s;
 }
 
-// dot products of one cached key with `cnt` (<= kMaxRep) queries that lie `dim` floats apart in shared memory
+// dot products of one cached key with `cnt` (<= kMaxRep) queries that lie `dim` floats apart in shared memory.  VEC: 16-byte
+// reads of the key and of the queries (dim * sizeof(T) is a multiple of 16 and everything is 16-byte aligned).
 template <typename T, bool VEC>
 __device__ __forceinline__ void key_dots(const T* __restrict__ key, const float* __restrict__ qs, int dim, int cnt, float* acc)
 {
@@ -137,6 +147,7 @@ __device__ __forceinline__ void key_dots(const T* __restrict__ key, const float*
     for (int u = 0; u < kMaxRep; ++u) acc[u] = 0.f;
     if (VEC) {
         constexpr int N = 16 / (int)sizeof(T);
+#pragma unroll 4                  // four 16-byte reads of the key in flight
         for (int d = 0; d < dim; d += N) {
             const uint4 raw = *reinterpret_cast<const uint4*>(key + d);
             const T* e = reinterpret_cast<const T*>(&raw);
@@ -146,9 +157,15 @@ __device__ __forceinline__ void key_dots(const T* __restrict__ key, const float*
 #pragma unroll
             for (int u = 0; u < kMaxRep; ++u) {
                 if (u < cnt) {
-                    const float* qu = qs + u * dim + d;
+                    const float4* qu = reinterpret_cast<const float4*>(qs + u * dim + d);
 #pragma unroll
-                    for (int i = 0; i < N; ++i) acc[u] = fmaf(qu[i], kv[i], acc[u]);
+                    for (int i = 0; i < N / 4; ++i) {
+                        const float4 q4 = qu[i];
+                        acc[u] = fmaf(q4.x, kv[4 * i], acc[u]);
+                        acc[u] = fmaf(q4.y, kv[4 * i + 1], acc[u]);
+                        acc[u] = fmaf(q4.z, kv[4 * i + 2], acc[u]);
+                        acc[u] = fmaf(q4.w, kv[4 * i + 3], acc[u]);
+                    }
                 }
             }
         }
@@ -162,6 +179,7 @@ __device__ __forceinline__ void key_dots(const T* __restrict__ key, const float*
     }
 }
 
+// address of position j's cache entry of the layer (its key row; the value row lies v_off bytes + its own row offset further)
 __device__ __forceinline__ const char* window_page(const WindowGeom& g, const int64_t* pages, int j)
 {
     return reinterpret_cast<const char*>(pages[j / g.block_len]) + g.layer_off;
@@ -175,147 +193,237 @@ __device__ __forceinline__ void merge_ml(float& m, float& l, float om, float ol)
     m = mx;
 }
 
-// Pass 1.  grid (rows, kv_heads, splits), 128 threads: thread i walks keys j0 + i, j0 + i + 128, ... of the range.
+// Pass 1.  grid (row blocks, kv_heads, splits), up to 128 threads: thread i walks keys j0 + i, j0 + i + blockDim, ... of the range
+// for all (row, head) pairs of the block's rows that belong to one sequence and of the heads that share key/value head blockIdx.y.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(128) window_stats_kernel(const float* __restrict__ qn, WindowGeom g, float* __restrict__ ml)
 {
     extern __shared__ __align__(16) float win_smem[];
     __shared__ float red_m[4][kMaxRep], red_l[4][kMaxRep];
-    const int t = blockIdx.x, c = blockIdx.y, z = blockIdx.z, tid = threadIdx.x;
-    const int rep = g.heads / g.kv_heads, s = g.tok_seq[t], pos = g.tok_pos[t];
-    float* qs = win_smem;                                                    // [rep][dim]
-    const float* qrow = qn + ((size_t)t * g.heads + (size_t)c * rep) * g.dim;
-    for (int i = tid; i < rep * g.dim; i += blockDim.x) qs[i] = qrow[i];
-    __syncthreads();
-    int j0, j1;
-    window_range(g, pos, z, j0, j1);
-    const int64_t* pages = g.block_ptrs + g.cu_blocks[s];
-    const size_t k_row = (size_t)g.kv_heads * g.dim;
-    for (int hb = 0; hb < rep; hb += kMaxRep) {
-        const int cnt = min(kMaxRep, rep - hb);
-        float m[kMaxRep], l[kMaxRep];
-#pragma unroll
-        for (int u = 0; u < kMaxRep; ++u) { m[u] = -1e30f; l[u] = 0.f; }
-        for (int j = j0 + tid; j < j1; j += blockDim.x) {
-            const T* key = reinterpret_cast<const T*>(window_page(g, pages, j)) + (size_t)(j % g.block_len) * k_row + (size_t)c * g.dim;
-            float acc[kMaxRep];
-            key_dots<T, VEC>(key, qs + hb * g.dim, g.dim, cnt, acc);
-#pragma unroll
-            for (int u = 0; u < kMaxRep; ++u) {
-                if (u < cnt) merge_ml(m[u], l[u], window_score(g, acc[u], c * rep + hb + u, pos - j), 1.0f);
-            }
-        }
-        // across the block: lanes of a warp by shuffles, the four warps through shared memory
-#pragma unroll
-        for (int u = 0; u < kMaxRep; ++u) {
-            for (int o = 16; o > 0; o >>= 1) {
-                const float om = __shfl_xor_sync(0xffffffffu, m[u], o), ol = __shfl_xor_sync(0xffffffffu, l[u], o);
-                merge_ml(m[u], l[u], om, ol);
-            }
+    const int c = blockIdx.y, z = blockIdx.z, tid = threadIdx.x, nw = blockDim.x >> 5;
+    const int H = g.heads, D = g.dim, rep = H / g.kv_heads;
+    const int t0 = blockIdx.x * g.rows, t1 = min(g.n, t0 + g.rows);
+    float* qs = win_smem;                                                    // [rows * rep][dim]
+    const size_t k_row = (size_t)g.kv_heads * D;
+    for (int ta = t0; ta < t1;) {
+        const int s = g.tok_seq[ta];
+        int tb = ta + 1;
+        while (tb < t1 && g.tok_seq[tb] == s) ++tb;
+        const int nr = tb - ta, pos = g.tok_pos[ta], pairs = nr * rep;
+        __syncthreads();
+        for (int i = tid; i < pairs * D; i += blockDim.x) {
+            const int u = i / D, d = i - u * D, r = u / rep, hh = u - r * rep;
+            qs[i] = qn[((size_t)(ta + r) * H + c * rep + hh) * D + d];
         }
         __syncthreads();
-        if ((tid & 31) == 0) {
+        int j0, j1;
+        window_range(g, pos, pos + nr - 1, z, j0, j1);
+        const int64_t* pages = g.block_ptrs + g.cu_blocks[s];
+        for (int ub = 0; ub < pairs; ub += kMaxRep) {
+            const int cnt = min(kMaxRep, pairs - ub);
+            float m[kMaxRep], l[kMaxRep];
 #pragma unroll
-            for (int u = 0; u < kMaxRep; ++u) { red_m[tid >> 5][u] = m[u]; red_l[tid >> 5][u] = l[u]; }
-        }
-        __syncthreads();
-        if (tid < cnt) {
-            float mm = red_m[0][tid], ll = red_l[0][tid];
-            for (int w = 1; w < 4; ++w) merge_ml(mm, ll, red_m[w][tid], red_l[w][tid]);
-            float* dst = ml + (((size_t)t * g.heads + c * rep + hb + tid) * g.splits + z) * 2;
-            dst[0] = mm;
-            dst[1] = ll;
-        }
-    }
-}
-
-// Pass 2.  grid (rows, splits), 256 threads.  Shared memory (floats): qs [heads][dim] | mx [heads] | linv [heads] |
-// talk [heads][heads] | p [heads][kWinTile] | p2 [heads][kWinTile] | o [heads][vdim].
-template <typename T, bool VEC>
-__global__ void __launch_bounds__(256) window_pv_kernel(const float* __restrict__ qn, WindowGeom g, const float* __restrict__ ml,
-                                                        float* __restrict__ o_part)
-{
-    extern __shared__ __align__(16) float win_smem[];
-    const int t = blockIdx.x, z = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
-    const int H = g.heads, G = g.kv_heads, rep = H / G, D = g.dim, V = g.vdim;
-    const int s = g.tok_seq[t], pos = g.tok_pos[t];
-    float* qs = win_smem;
-    float* mx = qs + (size_t)H * D;
-    float* linv = mx + H;
-    float* talk = linv + H;
-    float* p = talk + (g.talk ? H * H : 0);
-    float* p2 = g.talk ? p + H * kWinTile : p;
-    float* o = p2 + H * kWinTile;
-    for (int i = tid; i < H * D; i += nt) qs[i] = qn[(size_t)t * H * D + i];
-    for (int i = tid; i < H * V; i += nt) o[i] = 0.f;
-    if (g.talk)
-        for (int i = tid; i < H * H; i += nt) talk[i] = g.talk[i];
-    for (int h = tid; h < H; h += nt) {
-        const float* src = ml + ((size_t)t * H + h) * g.splits * 2;
-        float mm = src[0], ll = src[1];
-        for (int k = 1; k < g.splits; ++k) merge_ml(mm, ll, src[2 * k], src[2 * k + 1]);
-        mx[h] = mm;
-        linv[h] = 1.0f / ll;
-    }
-    __syncthreads();
-    int j0, j1;
-    window_range(g, pos, z, j0, j1);
-    const int64_t* pages = g.block_ptrs + g.cu_blocks[s];
-    const size_t k_row = (size_t)G * D, v_row = (size_t)G * V;
-    for (int jt = j0; jt < j1; jt += kWinTile) {
-        const int kt = min(kWinTile, j1 - jt);
-        // final softmax weights of every head for the tile's keys: one (key, key/value head) pair per thread
-        for (int item = tid; item < kt * G; item += nt) {
-            const int c = item / kt, jj = item % kt, j = jt + jj;
-            const T* key = reinterpret_cast<const T*>(window_page(g, pages, j)) + (size_t)(j % g.block_len) * k_row + (size_t)c * D;
-            for (int hb = 0; hb < rep; hb += kMaxRep) {
-                const int cnt = min(kMaxRep, rep - hb);
+            for (int u = 0; u < kMaxRep; ++u) { m[u] = -1e30f; l[u] = 0.f; }
+            for (int j = j0 + tid; j < j1; j += blockDim.x) {
+                const T* key = reinterpret_cast<const T*>(window_page(g, pages, j)) + (size_t)(j % g.block_len) * k_row + (size_t)c * D;
                 float acc[kMaxRep];
-                key_dots<T, VEC>(key, qs + (size_t)(c * rep + hb) * D, D, cnt, acc);
+                key_dots<T, VEC>(key, qs + (size_t)ub * D, D, cnt, acc);
 #pragma unroll
                 for (int u = 0; u < kMaxRep; ++u) {
                     if (u < cnt) {
-                        const int h = c * rep + hb + u;
-                        p[h * kWinTile + jj] = expf(window_score(g, acc[u], h, pos - j) - mx[h]) * linv[h];
+                        const int r = (ub + u) / rep, hh = (ub + u) - r * rep;
+                        if (window_sees(g, pos + r, j)) merge_ml(m[u], l[u], window_score(g, acc[u], c * rep + hh, pos + r - j), 1.0f);
+                    }
+                }
+            }
+            // across the block: lanes of a warp by shuffles, the warps through shared memory
+#pragma unroll
+            for (int u = 0; u < kMaxRep; ++u) {
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float om = __shfl_xor_sync(0xffffffffu, m[u], o), ol = __shfl_xor_sync(0xffffffffu, l[u], o);
+                    merge_ml(m[u], l[u], om, ol);
+                }
+            }
+            __syncthreads();
+            if ((tid & 31) == 0) {
+#pragma unroll
+                for (int u = 0; u < kMaxRep; ++u) { red_m[tid >> 5][u] = m[u]; red_l[tid >> 5][u] = l[u]; }
+            }
+            __syncthreads();
+            if (tid < cnt) {
+                float mm = red_m[0][tid], ll = red_l[0][tid];
+                for (int w = 1; w < nw; ++w) merge_ml(mm, ll, red_m[w][tid], red_l[w][tid]);
+                const int r = (ub + tid) / rep, hh = (ub + tid) - r * rep;
+                float* dst = ml + (((size_t)(ta + r) * H + c * rep + hh) * g.splits + z) * 2;
+                dst[0] = mm;
+                dst[1] = ll;
+            }
+        }
+        ta = tb;
+    }
+}
+
+// CW (1 or 4) consecutive values of a cached row as float
+template <typename T, int CW> __device__ __forceinline__ void load_cols(const T* __restrict__ src, float* out);
+template <> __device__ __forceinline__ void load_cols<float, 1>(const float* __restrict__ src, float* out) { out[0] = src[0]; }
+template <> __device__ __forceinline__ void load_cols<bf16, 1>(const bf16* __restrict__ src, float* out) { out[0] = to_f(src[0]); }
+template <> __device__ __forceinline__ void load_cols<float, 4>(const float* __restrict__ src, float* out)
+{
+    const float4 v = *reinterpret_cast<const float4*>(src);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+template <> __device__ __forceinline__ void load_cols<bf16, 4>(const bf16* __restrict__ src, float* out)
+{
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    const bf16* e = reinterpret_cast<const bf16*>(&raw);
+    out[0] = to_f(e[0]); out[1] = to_f(e[1]); out[2] = to_f(e[2]); out[3] = to_f(e[3]);
+}
+
+__device__ __forceinline__ int pad4(int v) { return (v + 3) & ~3; }
+
+// Pass 2.  grid (row blocks, splits), 256 threads.  Shared memory: the tile's key and value row addresses [2][tile], then floats
+// qs [kv_heads][rows * rep][dim] | mx [rows * heads] | linv [rows * heads] | talk [heads][heads] | p [rows * heads][tile] |
+// p2 [rows * heads][tile] | o [rows * heads][vdim] (every part padded to a multiple of four floats).
+// CW: value columns per thread and walk (4: 8- or 16-byte reads of the values).
+template <typename T, bool VEC, int CW>
+__global__ void __launch_bounds__(256) window_pv_kernel(const float* __restrict__ qn, WindowGeom g, const float* __restrict__ ml,
+                                                        float* __restrict__ o_part)
+{
+    extern __shared__ __align__(16) unsigned char win_raw[];
+    const int z = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
+    const int H = g.heads, G = g.kv_heads, rep = H / G, D = g.dim, V = g.vdim, KT = g.tile, maxpairs = g.rows * rep;
+    const char** krow = reinterpret_cast<const char**>(win_raw);
+    const char** vrow = krow + KT;
+    float* qs = reinterpret_cast<float*>(win_raw + (size_t)2 * KT * sizeof(char*));
+    float* mx = qs + pad4(g.rows * H * D);
+    float* linv = mx + pad4(g.rows * H);
+    float* talk = linv + pad4(g.rows * H);
+    float* p = talk + (g.talk ? pad4(H * H) : 0);
+    float* p2 = g.talk ? p + (size_t)g.rows * H * KT : p;
+    float* o = p2 + (size_t)g.rows * H * KT;
+    if (g.talk)
+        for (int i = tid; i < H * H; i += nt) talk[i] = g.talk[i];
+    const int t0 = blockIdx.x * g.rows, t1 = min(g.n, t0 + g.rows);
+    const size_t k_row = (size_t)G * D * sizeof(T), v_row = (size_t)G * V * sizeof(T);
+    for (int ta = t0; ta < t1;) {
+        const int s = g.tok_seq[ta];
+        int tb = ta + 1;
+        while (tb < t1 && g.tok_seq[tb] == s) ++tb;
+        const int nr = tb - ta, pos = g.tok_pos[ta], pairs = nr * rep;
+        __syncthreads();
+        for (int i = tid; i < nr * H * D; i += nt) {
+            const int rh = i / D, d = i - rh * D, r = rh / H, h = rh - r * H, c = h / rep, hh = h - c * rep;
+            qs[((size_t)c * maxpairs + r * rep + hh) * D + d] = qn[(size_t)ta * H * D + i];
+        }
+        for (int i = tid; i < nr * H * V; i += nt) o[i] = 0.f;
+        for (int i = tid; i < nr * H; i += nt) {
+            const float* src = ml + ((size_t)ta * H + i) * g.splits * 2;
+            float mm = src[0], ll = src[1];
+            for (int k = 1; k < g.splits; ++k) merge_ml(mm, ll, src[2 * k], src[2 * k + 1]);
+            mx[i] = mm;
+            linv[i] = 1.0f / ll;
+        }
+        int j0, j1;
+        window_range(g, pos, pos + nr - 1, z, j0, j1);
+        const int64_t* pages = g.block_ptrs + g.cu_blocks[s];
+        for (int jt = j0; jt < j1; jt += KT) {
+            const int kt = min(KT, j1 - jt), kt4 = pad4(kt);
+            __syncthreads();                      // the previous tile's readers are done; qs / mx / o of this segment are in place
+            for (int jj = tid; jj < kt; jj += nt) {
+                const int j = jt + jj;
+                const char* page = window_page(g, pages, j);
+                krow[jj] = page + (size_t)(j % g.block_len) * k_row;
+                vrow[jj] = page + g.v_off + (size_t)(j % g.block_len) * v_row;
+            }
+            for (int i = tid; i < nr * H * (kt4 - kt); i += nt) {          // weights of the keys that pad the tile to four
+                const int rh = i / (kt4 - kt);
+                p[(size_t)rh * KT + kt + (i - rh * (kt4 - kt))] = 0.f;
+            }
+            __syncthreads();
+            // final softmax weights of every (row, head) for the tile's keys: one (key, key/value head) pair per thread
+            for (int item = tid; item < kt * G; item += nt) {
+                const int c = item / kt, jj = item - c * kt, j = jt + jj;
+                const T* key = reinterpret_cast<const T*>(krow[jj]) + (size_t)c * D;
+                for (int ub = 0; ub < pairs; ub += kMaxRep) {
+                    const int cnt = min(kMaxRep, pairs - ub);
+                    float acc[kMaxRep];
+                    key_dots<T, VEC>(key, qs + ((size_t)c * maxpairs + ub) * D, D, cnt, acc);
+#pragma unroll
+                    for (int u = 0; u < kMaxRep; ++u) {
+                        if (u < cnt) {
+                            const int r = (ub + u) / rep, h = c * rep + (ub + u) - r * rep, rh = r * H + h;
+                            p[(size_t)rh * KT + jj] =
+                                window_sees(g, pos + r, j) ? expf(window_score(g, acc[u], h, pos + r - j) - mx[rh]) * linv[rh] : 0.f;
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+            if (g.talk) {
+                for (int item = tid; item < nr * H * kt4; item += nt) {
+                    const int rh = item / kt4, jj = item - rh * kt4, r = rh / H, h = rh - r * H;
+                    const float* pr = p + (size_t)r * H * KT + jj;
+                    float a = 0.f;
+                    for (int k = 0; k < H; ++k) a = fmaf(talk[h * H + k], pr[(size_t)k * KT], a);
+                    p2[(size_t)rh * KT + jj] = a;
+                }
+                __syncthreads();
+            }
+            // weighted value sums: one (key/value head, CW value columns) item per thread and walk, each value read once for the
+            // rows and heads that share it, four keys per step
+            const int ncg = V / CW;
+            for (int item = tid; item < G * ncg; item += nt) {
+                const int c = item / ncg, col = (item - c * ncg) * CW;
+                for (int ub = 0; ub < pairs; ub += kMaxRep) {
+                    const int cnt = min(kMaxRep, pairs - ub);
+                    float acc[kMaxRep][CW];
+                    int rhs[kMaxRep];
+#pragma unroll
+                    for (int u = 0; u < kMaxRep; ++u) {
+                        const int r = (ub + u) / rep;
+                        rhs[u] = r * H + c * rep + (ub + u) - r * rep;
+#pragma unroll
+                        for (int k = 0; k < CW; ++k) acc[u][k] = 0.f;
+                    }
+#pragma unroll 2                  // eight value reads in flight
+                    for (int jj = 0; jj < kt; jj += 4) {
+                        float vv[4][CW];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            if (jj + q < kt) load_cols<T, CW>(reinterpret_cast<const T*>(vrow[jj + q]) + (size_t)c * V + col, vv[q]);
+                            else {
+#pragma unroll
+                                for (int k = 0; k < CW; ++k) vv[q][k] = 0.f;
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < kMaxRep; ++u) {
+                            if (u < cnt) {
+                                const float4 w4 = *reinterpret_cast<const float4*>(p2 + (size_t)rhs[u] * KT + jj);
+#pragma unroll
+                                for (int k = 0; k < CW; ++k)
+                                    acc[u][k] += (w4.x * vv[0][k] + w4.y * vv[1][k]) + (w4.z * vv[2][k] + w4.w * vv[3][k]);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < kMaxRep; ++u) {
+                        if (u < cnt) {
+#pragma unroll
+                            for (int k = 0; k < CW; ++k) o[(size_t)rhs[u] * V + col + k] += acc[u][k];
+                        }
                     }
                 }
             }
         }
         __syncthreads();
-        if (g.talk) {
-            for (int item = tid; item < H * kt; item += nt) {
-                const int h = item / kt, jj = item % kt;
-                float a = 0.f;
-                for (int k = 0; k < H; ++k) a = fmaf(talk[h * H + k], p[k * kWinTile + jj], a);
-                p2[h * kWinTile + jj] = a;
-            }
-            __syncthreads();
+        float* dst = o_part + ((size_t)ta * g.splits + z) * H * V;          // row r of the segment: ((ta + r) * splits + z) * H * V
+        for (int i = tid; i < nr * H * V; i += nt) {
+            const int r = i / (H * V);
+            dst[(size_t)r * g.splits * H * V + (i - r * H * V)] = o[i];
         }
-        // weighted value sums: one (key/value head, value column) pair per thread, each value read once for the heads that share it
-        for (int item = tid; item < G * V; item += nt) {
-            const int c = item / V, col = item % V;
-            for (int hb = 0; hb < rep; hb += kMaxRep) {
-                const int cnt = min(kMaxRep, rep - hb);
-                float acc[kMaxRep];
-#pragma unroll
-                for (int u = 0; u < kMaxRep; ++u) acc[u] = 0.f;
-                for (int jj = 0; jj < kt; ++jj) {
-                    const int j = jt + jj;
-                    const T* val = reinterpret_cast<const T*>(window_page(g, pages, j) + g.v_off) + (size_t)(j % g.block_len) * v_row;
-                    const float vv = to_f(val[(size_t)c * V + col]);
-#pragma unroll
-                    for (int u = 0; u < kMaxRep; ++u)
-                        if (u < cnt) acc[u] = fmaf(p2[(c * rep + hb + u) * kWinTile + jj], vv, acc[u]);
-                }
-#pragma unroll
-                for (int u = 0; u < kMaxRep; ++u)
-                    if (u < cnt) o[(size_t)(c * rep + hb + u) * V + col] += acc[u];
-            }
-        }
-        __syncthreads();
+        ta = tb;
     }
-    float* dst = o_part + ((size_t)t * g.splits + z) * H * V;
-    for (int i = tid; i < H * V; i += nt) dst[i] = o[i];
 }
 
 // y[t, i] = (sum over ranges of o_part[t, z, i]) * sigmoid(gate[t, i]) as T

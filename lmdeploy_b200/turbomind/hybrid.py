@@ -446,10 +446,10 @@ class HybridModel:
 
     def window_splits(self, n, window, max_pos):
         """Key ranges per row of a windowed-attention launch: one for prompt portions; a step of few rows cuts its window into
-        ranges of at least 32 keys until the launch has about two blocks per SM.  A power of two (the engine keys its decode
+        ranges of at least 32 keys until the launch has about eight blocks per SM.  A power of two (the engine keys its decode
         graphs on it)."""
         keys = min(window, max_pos + 1) if window else max_pos + 1
-        want = min(296 // max(n, 1), keys // 32, 64)
+        want = min(1184 // max(n, 1), keys // 32, 64)
         splits = 1
         while splits * 2 <= want:
             splits *= 2
