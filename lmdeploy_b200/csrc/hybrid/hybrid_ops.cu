@@ -1030,6 +1030,24 @@ static size_t window_pv_smem(const b200h_window_args* a, int rows, int tile)
            sizeof(float) * (pad4(rh * a->dim) + 2 * pad4(rh) + (a->talk ? pad4(H * H) : 0) + (size_t)(a->talk ? 2 : 1) * rh * tile + rh * a->vdim);
 }
 
+struct WindowLaunch {
+    int blocks, stats_threads;
+    size_t stats_smem, pv_smem;
+};
+
+template <typename T, bool VEC, int CW, int NP>
+static void launch_window_kernels(const b200h_window_args* a, const WindowGeom& g, const WindowLaunch& l, cudaStream_t st)
+{
+    if (l.stats_smem > 48 * 1024)
+        cudaFuncSetAttribute(window_stats_kernel<T, VEC, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)l.stats_smem);
+    if (l.pv_smem > 48 * 1024)
+        cudaFuncSetAttribute(window_pv_kernel<T, VEC, CW, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)l.pv_smem);
+    window_stats_kernel<T, VEC, NP><<<dim3(l.blocks, a->kv_heads, a->splits), l.stats_threads, l.stats_smem, st>>>((const float*)a->qn, g,
+                                                                                                                   (float*)a->ml);
+    window_pv_kernel<T, VEC, CW, NP><<<dim3(l.blocks, a->splits), 256, l.pv_smem, st>>>((const float*)a->qn, g, (const float*)a->ml,
+                                                                                        (float*)a->o_part);
+}
+
 template <typename T, bool VEC, int CW>
 static int launch_window_attention(const b200h_window_args* a, WindowGeom g, cudaStream_t st)
 {
@@ -1042,19 +1060,19 @@ static int launch_window_attention(const b200h_window_args* a, WindowGeom g, cud
     g.tile = g.tile < 32 ? 32 : (g.tile > 128 ? 128 : g.tile);
     while (window_pv_smem(a, g.rows, g.tile) > budget && g.tile > 32) g.tile /= 2;
     while (window_pv_smem(a, g.rows, g.tile) > budget && g.rows > 1) g.rows /= 2;
-    const size_t stats_smem = (size_t)g.rows * rep * a->dim * sizeof(float), pv_smem = window_pv_smem(a, g.rows, g.tile);
-    if (stats_smem > 200 * 1024 || pv_smem > 200 * 1024)
+    WindowLaunch l;
+    l.stats_smem = (size_t)g.rows * rep * a->dim * sizeof(float);
+    l.pv_smem = window_pv_smem(a, g.rows, g.tile);
+    if (l.stats_smem > 200 * 1024 || l.pv_smem > 200 * 1024)
         return fail(B200H_ERR_UNSUPPORTED, "window_attention: heads * (dim + vdim + heads) floats exceed an SM's shared memory");
-    if (stats_smem > 48 * 1024)
-        cudaFuncSetAttribute(window_stats_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stats_smem);
-    if (pv_smem > 48 * 1024)
-        cudaFuncSetAttribute(window_pv_kernel<T, VEC, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pv_smem);
-    const int blocks = (a->n + g.rows - 1) / g.rows;
+    l.blocks = (a->n + g.rows - 1) / g.rows;
     // pass 1: a thread per key of the range, at most 128
     const int keys = a->window > 0 ? a->window + g.rows - 1 : 1 << 30, per = (keys + a->splits - 1) / a->splits;
-    const int stats_threads = per <= 32 ? 32 : (per <= 64 ? 64 : 128);
-    window_stats_kernel<T, VEC><<<dim3(blocks, a->kv_heads, a->splits), stats_threads, stats_smem, st>>>((const float*)a->qn, g, (float*)a->ml);
-    window_pv_kernel<T, VEC, CW><<<dim3(blocks, a->splits), 256, pv_smem, st>>>((const float*)a->qn, g, (const float*)a->ml, (float*)a->o_part);
+    l.stats_threads = per <= 32 ? 32 : (per <= 64 ? 64 : 128);
+    const int pairs = g.rows * rep;              // (row, head) pairs that share a key: walked NP at a time
+    if (pairs <= 2) launch_window_kernels<T, VEC, CW, 2>(a, g, l, st);
+    else if (pairs <= 4) launch_window_kernels<T, VEC, CW, 4>(a, g, l, st);
+    else launch_window_kernels<T, VEC, CW, 8>(a, g, l, st);
     window_out_kernel<T><<<a->n, 256, 0, st>>>((const float*)a->o_part, a->splits, H * a->vdim, (const T*)a->gate, a->ld_gate, (T*)a->y);
     return 0;
 }

@@ -19,7 +19,7 @@
 // cached key or value is read and converted once for all of them (prompt portions: 4 rows; a step of single tokens: 1).
 // Scores, softmax, recombination and the weighted value sums are float whatever T is.
 
-constexpr int kMaxRep = 8;              // query heads of one key/value head handled per walk over a key
+constexpr int kMaxPairs = 8;            // most (row, head) pairs handled per walk over a key: the kernels' template parameter NP
 
 // x[t] += table[idx ? idx[t] : fixed]
 template <typename T>
@@ -138,13 +138,13 @@ __device__ __forceinline__ float window_score(const WindowGeom& g, float dot, in
     return s;
 }
 
-// dot products of one cached key with `cnt` (<= kMaxRep) queries that lie `dim` floats apart in shared memory.  VEC: 16-byte
+// dot products of one cached key with `cnt` (<= NP) queries that lie `dim` floats apart in shared memory.  VEC: 16-byte
 // reads of the key and of the queries (dim * sizeof(T) is a multiple of 16 and everything is 16-byte aligned).
-template <typename T, bool VEC>
+template <typename T, bool VEC, int NP>
 __device__ __forceinline__ void key_dots(const T* __restrict__ key, const float* __restrict__ qs, int dim, int cnt, float* acc)
 {
 #pragma unroll
-    for (int u = 0; u < kMaxRep; ++u) acc[u] = 0.f;
+    for (int u = 0; u < NP; ++u) acc[u] = 0.f;
     if (VEC) {
         constexpr int N = 16 / (int)sizeof(T);
 #pragma unroll 4                  // four 16-byte reads of the key in flight
@@ -155,7 +155,7 @@ __device__ __forceinline__ void key_dots(const T* __restrict__ key, const float*
 #pragma unroll
             for (int i = 0; i < N; ++i) kv[i] = to_f(e[i]);
 #pragma unroll
-            for (int u = 0; u < kMaxRep; ++u) {
+            for (int u = 0; u < NP; ++u) {
                 if (u < cnt) {
                     const float4* qu = reinterpret_cast<const float4*>(qs + u * dim + d);
 #pragma unroll
@@ -173,7 +173,7 @@ __device__ __forceinline__ void key_dots(const T* __restrict__ key, const float*
         for (int d = 0; d < dim; ++d) {
             const float kv = to_f(key[d]);
 #pragma unroll
-            for (int u = 0; u < kMaxRep; ++u)
+            for (int u = 0; u < NP; ++u)
                 if (u < cnt) acc[u] = fmaf(qs[u * dim + d], kv, acc[u]);
         }
     }
@@ -195,11 +195,11 @@ __device__ __forceinline__ void merge_ml(float& m, float& l, float om, float ol)
 
 // Pass 1.  grid (row blocks, kv_heads, splits), up to 128 threads: thread i walks keys j0 + i, j0 + i + blockDim, ... of the range
 // for all (row, head) pairs of the block's rows that belong to one sequence and of the heads that share key/value head blockIdx.y.
-template <typename T, bool VEC>
+template <typename T, bool VEC, int NP>
 __global__ void __launch_bounds__(128) window_stats_kernel(const float* __restrict__ qn, WindowGeom g, float* __restrict__ ml)
 {
     extern __shared__ __align__(16) float win_smem[];
-    __shared__ float red_m[4][kMaxRep], red_l[4][kMaxRep];
+    __shared__ float red_m[4][kMaxPairs], red_l[4][kMaxPairs];
     const int c = blockIdx.y, z = blockIdx.z, tid = threadIdx.x, nw = blockDim.x >> 5;
     const int H = g.heads, D = g.dim, rep = H / g.kv_heads;
     const int t0 = blockIdx.x * g.rows, t1 = min(g.n, t0 + g.rows);
@@ -219,17 +219,17 @@ __global__ void __launch_bounds__(128) window_stats_kernel(const float* __restri
         int j0, j1;
         window_range(g, pos, pos + nr - 1, z, j0, j1);
         const int64_t* pages = g.block_ptrs + g.cu_blocks[s];
-        for (int ub = 0; ub < pairs; ub += kMaxRep) {
-            const int cnt = min(kMaxRep, pairs - ub);
-            float m[kMaxRep], l[kMaxRep];
+        for (int ub = 0; ub < pairs; ub += NP) {
+            const int cnt = min(NP, pairs - ub);
+            float m[NP], l[NP];
 #pragma unroll
-            for (int u = 0; u < kMaxRep; ++u) { m[u] = -1e30f; l[u] = 0.f; }
+            for (int u = 0; u < NP; ++u) { m[u] = -1e30f; l[u] = 0.f; }
             for (int j = j0 + tid; j < j1; j += blockDim.x) {
                 const T* key = reinterpret_cast<const T*>(window_page(g, pages, j)) + (size_t)(j % g.block_len) * k_row + (size_t)c * D;
-                float acc[kMaxRep];
-                key_dots<T, VEC>(key, qs + (size_t)ub * D, D, cnt, acc);
+                float acc[NP];
+                key_dots<T, VEC, NP>(key, qs + (size_t)ub * D, D, cnt, acc);
 #pragma unroll
-                for (int u = 0; u < kMaxRep; ++u) {
+                for (int u = 0; u < NP; ++u) {
                     if (u < cnt) {
                         const int r = (ub + u) / rep, hh = (ub + u) - r * rep;
                         if (window_sees(g, pos + r, j)) merge_ml(m[u], l[u], window_score(g, acc[u], c * rep + hh, pos + r - j), 1.0f);
@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(128) window_stats_kernel(const float* __restri
             }
             // across the block: lanes of a warp by shuffles, the warps through shared memory
 #pragma unroll
-            for (int u = 0; u < kMaxRep; ++u) {
+            for (int u = 0; u < NP; ++u) {
                 for (int o = 16; o > 0; o >>= 1) {
                     const float om = __shfl_xor_sync(0xffffffffu, m[u], o), ol = __shfl_xor_sync(0xffffffffu, l[u], o);
                     merge_ml(m[u], l[u], om, ol);
@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(128) window_stats_kernel(const float* __restri
             __syncthreads();
             if ((tid & 31) == 0) {
 #pragma unroll
-                for (int u = 0; u < kMaxRep; ++u) { red_m[tid >> 5][u] = m[u]; red_l[tid >> 5][u] = l[u]; }
+                for (int u = 0; u < NP; ++u) { red_m[tid >> 5][u] = m[u]; red_l[tid >> 5][u] = l[u]; }
             }
             __syncthreads();
             if (tid < cnt) {
@@ -284,8 +284,9 @@ __device__ __forceinline__ int pad4(int v) { return (v + 3) & ~3; }
 // Pass 2.  grid (row blocks, splits), 256 threads.  Shared memory: the tile's key and value row addresses [2][tile], then floats
 // qs [kv_heads][rows * rep][dim] | mx [rows * heads] | linv [rows * heads] | talk [heads][heads] | p [rows * heads][tile] |
 // p2 [rows * heads][tile] | o [rows * heads][vdim] (every part padded to a multiple of four floats).
-// CW: value columns per thread and walk (4: 8- or 16-byte reads of the values).
-template <typename T, bool VEC, int CW>
+// CW: value columns per thread and walk (4: 8- or 16-byte reads of the values).  NP: (row, head) pairs per walk over a key or a
+// value -- 2 for a step of single tokens with two heads per key/value head, which keeps registers low and more blocks resident.
+template <typename T, bool VEC, int CW, int NP>
 __global__ void __launch_bounds__(256) window_pv_kernel(const float* __restrict__ qn, WindowGeom g, const float* __restrict__ ml,
                                                         float* __restrict__ o_part)
 {
@@ -344,12 +345,12 @@ __global__ void __launch_bounds__(256) window_pv_kernel(const float* __restrict_
             for (int item = tid; item < kt * G; item += nt) {
                 const int c = item / kt, jj = item - c * kt, j = jt + jj;
                 const T* key = reinterpret_cast<const T*>(krow[jj]) + (size_t)c * D;
-                for (int ub = 0; ub < pairs; ub += kMaxRep) {
-                    const int cnt = min(kMaxRep, pairs - ub);
-                    float acc[kMaxRep];
-                    key_dots<T, VEC>(key, qs + ((size_t)c * maxpairs + ub) * D, D, cnt, acc);
+                for (int ub = 0; ub < pairs; ub += NP) {
+                    const int cnt = min(NP, pairs - ub);
+                    float acc[NP];
+                    key_dots<T, VEC, NP>(key, qs + ((size_t)c * maxpairs + ub) * D, D, cnt, acc);
 #pragma unroll
-                    for (int u = 0; u < kMaxRep; ++u) {
+                    for (int u = 0; u < NP; ++u) {
                         if (u < cnt) {
                             const int r = (ub + u) / rep, h = c * rep + (ub + u) - r * rep, rh = r * H + h;
                             p[(size_t)rh * KT + jj] =
@@ -374,12 +375,12 @@ __global__ void __launch_bounds__(256) window_pv_kernel(const float* __restrict_
             const int ncg = V / CW;
             for (int item = tid; item < G * ncg; item += nt) {
                 const int c = item / ncg, col = (item - c * ncg) * CW;
-                for (int ub = 0; ub < pairs; ub += kMaxRep) {
-                    const int cnt = min(kMaxRep, pairs - ub);
-                    float acc[kMaxRep][CW];
-                    int rhs[kMaxRep];
+                for (int ub = 0; ub < pairs; ub += NP) {
+                    const int cnt = min(NP, pairs - ub);
+                    float acc[NP][CW];
+                    int rhs[NP];
 #pragma unroll
-                    for (int u = 0; u < kMaxRep; ++u) {
+                    for (int u = 0; u < NP; ++u) {
                         const int r = (ub + u) / rep;
                         rhs[u] = r * H + c * rep + (ub + u) - r * rep;
 #pragma unroll
@@ -397,7 +398,7 @@ __global__ void __launch_bounds__(256) window_pv_kernel(const float* __restrict_
                             }
                         }
 #pragma unroll
-                        for (int u = 0; u < kMaxRep; ++u) {
+                        for (int u = 0; u < NP; ++u) {
                             if (u < cnt) {
                                 const float4 w4 = *reinterpret_cast<const float4*>(p2 + (size_t)rhs[u] * KT + jj);
 #pragma unroll
@@ -407,10 +408,17 @@ __global__ void __launch_bounds__(256) window_pv_kernel(const float* __restrict_
                         }
                     }
 #pragma unroll
-                    for (int u = 0; u < kMaxRep; ++u) {
+                    for (int u = 0; u < NP; ++u) {
                         if (u < cnt) {
+                            float* dst = o + (size_t)rhs[u] * V + col;
+                            if (CW == 4) {                     // one 16-byte read and write per lane: no bank conflicts
+                                float4 cur = *reinterpret_cast<float4*>(dst);
+                                cur.x += acc[u][0]; cur.y += acc[u][CW > 1 ? 1 : 0]; cur.z += acc[u][CW > 2 ? 2 : 0]; cur.w += acc[u][CW > 3 ? 3 : 0];
+                                *reinterpret_cast<float4*>(dst) = cur;
+                            } else {
 #pragma unroll
-                            for (int k = 0; k < CW; ++k) o[(size_t)rhs[u] * V + col + k] += acc[u][k];
+                                for (int k = 0; k < CW; ++k) dst[k] += acc[u][k];
+                            }
                         }
                     }
                 }
