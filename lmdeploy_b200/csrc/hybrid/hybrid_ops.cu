@@ -1073,7 +1073,8 @@ static int launch_window_attention(const b200h_window_args* a, WindowGeom g, cud
     if (pairs <= 2) launch_window_kernels<T, VEC, CW, 2>(a, g, l, st);
     else if (pairs <= 4) launch_window_kernels<T, VEC, CW, 4>(a, g, l, st);
     else launch_window_kernels<T, VEC, CW, 8>(a, g, l, st);
-    window_out_kernel<T><<<a->n, 256, 0, st>>>((const float*)a->o_part, a->splits, H * a->vdim, (const T*)a->gate, a->ld_gate, (T*)a->y);
+    window_out_kernel<T><<<dim3(a->n, (H * a->vdim + 255) / 256), 256, 0, st>>>((const float*)a->o_part, a->splits, H * a->vdim, (const T*)a->gate,
+                                                                                a->ld_gate, (T*)a->y);
     return 0;
 }
 

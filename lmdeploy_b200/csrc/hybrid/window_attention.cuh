@@ -439,11 +439,12 @@ template <typename T>
 __global__ void window_out_kernel(const float* __restrict__ o_part, int splits, int cols, const T* __restrict__ gate, int64_t ld_gate,
                                   T* __restrict__ y)
 {
-    const int t = blockIdx.x;
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-        float a = 0.f;
-        for (int z = 0; z < splits; ++z) a += o_part[((size_t)t * splits + z) * cols + i];
-        if (gate) a *= sigmoid_f(to_f(gate[(size_t)t * ld_gate + i]));
-        y[(size_t)t * cols + i] = from_f<T>(a);
-    }
+    const int t = blockIdx.x, i = blockIdx.y * blockDim.x + threadIdx.x;          // one column per thread
+    if (i >= cols) return;
+    const float* src = o_part + (size_t)t * splits * cols + i;
+    float a = 0.f;
+#pragma unroll 8
+    for (int z = 0; z < splits; ++z) a += src[(size_t)z * cols];
+    if (gate) a *= sigmoid_f(to_f(gate[(size_t)t * ld_gate + i]));
+    y[(size_t)t * cols + i] = from_f<T>(a);
 }
