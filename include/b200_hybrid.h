@@ -45,6 +45,7 @@ typedef struct b200h_window_args {
     const void* k;           /* T [n, ld]: kv_heads * dim columns */
     const void* v;           /* T [n, ld]: kv_heads * vdim columns */
     int64_t ld;
+    const void* bias;        /* float [heads * dim + kv_heads * dim + kv_heads * vdim] or NULL: added to q | k | v before anything else */
     const void* q_norm;      /* float [heads * dim] or NULL: RMS norm over the whole query projection */
     const void* k_norm;      /* float [kv_heads * dim] or NULL */
     void* qn;                /* float [n, heads * dim]: out of b200h_window_prep */
@@ -64,7 +65,7 @@ typedef struct b200h_window_args {
     int dtype;
     void* stream;
 } b200h_window_args;
-/* Norm of query and key, cache store of key and value (fills qn). */
+/* Bias, norm of query and key, cache store of key and value (fills qn). */
 B200H_API int b200h_window_prep(const b200h_window_args* args);
 /* Attention of the step's rows over the cache (fills y); the step's own rows must have been stored by b200h_window_prep. */
 B200H_API int b200h_window_attention(const b200h_window_args* args);
@@ -217,6 +218,7 @@ typedef struct b200h_window_args {
     const void* k;           /* T [n, ld]: kv_heads * dim columns */
     const void* v;           /* T [n, ld]: kv_heads * vdim columns */
     int64_t ld;
+    const void* bias;        /* float [heads * dim + kv_heads * dim + kv_heads * vdim] or NULL: added to q | k | v before anything else */
     const void* q_norm;      /* float [heads * dim] or NULL: RMS norm over the whole query projection */
     const void* k_norm;      /* float [kv_heads * dim] or NULL */
     void* qn;                /* float [n, heads * dim]: out of b200h_window_prep */
@@ -236,7 +238,7 @@ typedef struct b200h_window_args {
     int dtype;
     void* stream;
 } b200h_window_args;
-/* Norm of query and key, cache store of key and value (fills qn). */
+/* Bias, norm of query and key, cache store of key and value (fills qn). */
 B200H_API int b200h_window_prep(const b200h_window_args* args);
 /* Attention of the step's rows over the cache (fills y); the step's own rows must have been stored by b200h_window_prep. */
 B200H_API int b200h_window_attention(const b200h_window_args* args);

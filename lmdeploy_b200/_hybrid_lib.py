@@ -43,7 +43,7 @@ class WindowArgs(C.Structure):
         ("n", C.c_int), ("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("block_len", C.c_int),
         ("window", C.c_int), ("splits", C.c_int), ("scale", C.c_float), ("softcap", C.c_float), ("eps", C.c_float),
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("ld", C.c_int64),
-        ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("qn", C.c_void_p),
+        ("bias", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("qn", C.c_void_p),
         ("r1", C.c_void_p), ("r2", C.c_void_p), ("talk", C.c_void_p), ("gate", C.c_void_p), ("ld_gate", C.c_int64),
         ("ml", C.c_void_p), ("o_part", C.c_void_p), ("y", C.c_void_p),
         ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("block_ptrs", C.c_void_p), ("cu_blocks", C.c_void_p),

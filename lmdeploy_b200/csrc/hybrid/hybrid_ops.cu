@@ -1017,7 +1017,7 @@ B200H_API int b200h_window_prep(const b200h_window_args* a)
     cudaStream_t st = (cudaStream_t)a->stream;
     B200H_DISPATCH_T(a->dtype, window_prep_kernel<T><<<a->n, 256, 0, st>>>(
         (const T*)a->q, (const T*)a->k, (const T*)a->v, a->ld, a->heads * a->dim, a->kv_heads * a->dim, a->kv_heads * a->vdim,
-        (const float*)a->q_norm, (const float*)a->k_norm, a->eps, (const int*)a->tok_seq, (const int*)a->tok_pos,
+        (const float*)a->bias, (const float*)a->q_norm, (const float*)a->k_norm, a->eps, (const int*)a->tok_seq, (const int*)a->tok_pos,
         (const int64_t*)a->block_ptrs, (const int*)a->cu_blocks, a->layer_off, a->v_off, a->block_len, (float*)a->qn));
     return launched("window_prep");
 }

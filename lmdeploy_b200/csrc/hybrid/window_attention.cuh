@@ -61,27 +61,33 @@ __global__ void relu2_kernel(T* __restrict__ x, int64_t count)
     x[i] = from_f<T>(v * v);
 }
 
-// One block per row: the query is normed over all its heads at once (-> qn, float), the key likewise and written to the row's
-// cache entry as T, the value is copied to the cache.  wq / wk == nullptr: no norm of that projection.
+// One block per row: the projections' biases are added (float), the query is normed over all its heads at once (-> qn, float), the
+// key likewise and written to the row's cache entry as T, the value is written to the cache.  wq / wk == nullptr: no norm of that
+// projection; bias (q | k | v entries, float) == nullptr: none.
 template <typename T>
 __global__ void window_prep_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int64_t ld, int q_cols,
-                                   int k_cols, int v_cols, const float* __restrict__ wq, const float* __restrict__ wk, float eps,
-                                   const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, const int64_t* __restrict__ block_ptrs,
-                                   const int* __restrict__ cu_blocks, int64_t layer_off, int64_t v_off, int block_len,
-                                   float* __restrict__ qn)
+                                   int k_cols, int v_cols, const float* __restrict__ bias, const float* __restrict__ wq,
+                                   const float* __restrict__ wk, float eps, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                   const int64_t* __restrict__ block_ptrs, const int* __restrict__ cu_blocks, int64_t layer_off, int64_t v_off,
+                                   int block_len, float* __restrict__ qn)
 {
     __shared__ float red[32];
     const int t = blockIdx.x, s = tok_seq[t], pos = tok_pos[t];
+    const float* bq = bias;
+    const float* bk = bias ? bias + q_cols : nullptr;
+    const float* bv = bias ? bias + q_cols + k_cols : nullptr;
     const T* qr = q + (size_t)t * ld;
     float r = 1.0f;
     if (wq) {
         float ss = 0.f;
-        for (int i = threadIdx.x; i < q_cols; i += blockDim.x) { const float a = to_f(qr[i]); ss += a * a; }
+        for (int i = threadIdx.x; i < q_cols; i += blockDim.x) { const float a = to_f(qr[i]) + (bq ? bq[i] : 0.f); ss += a * a; }
         ss = block_sum(ss, red);
         r = 1.0f / sqrtf(ss / (float)q_cols + eps);
     }
-    for (int i = threadIdx.x; i < q_cols; i += blockDim.x) qn[(size_t)t * q_cols + i] = wq ? to_f(qr[i]) * r * wq[i] : to_f(qr[i]);
-
+    for (int i = threadIdx.x; i < q_cols; i += blockDim.x) {
+        const float a = to_f(qr[i]) + (bq ? bq[i] : 0.f);
+        qn[(size_t)t * q_cols + i] = wq ? a * r * wq[i] : a;
+    }
     char* page = reinterpret_cast<char*>(block_ptrs[cu_blocks[s] + pos / block_len]) + layer_off;
     const int at = pos % block_len;
     const T* kr = k + (size_t)t * ld;
@@ -89,14 +95,17 @@ __global__ void window_prep_kernel(const T* __restrict__ q, const T* __restrict_
     r = 1.0f;
     if (wk) {
         float ss = 0.f;
-        for (int i = threadIdx.x; i < k_cols; i += blockDim.x) { const float a = to_f(kr[i]); ss += a * a; }
+        for (int i = threadIdx.x; i < k_cols; i += blockDim.x) { const float a = to_f(kr[i]) + (bk ? bk[i] : 0.f); ss += a * a; }
         ss = block_sum(ss, red);
         r = 1.0f / sqrtf(ss / (float)k_cols + eps);
     }
-    for (int i = threadIdx.x; i < k_cols; i += blockDim.x) k_dst[i] = wk ? from_f<T>(to_f(kr[i]) * r * wk[i]) : kr[i];
+    for (int i = threadIdx.x; i < k_cols; i += blockDim.x) {
+        const float a = to_f(kr[i]) + (bk ? bk[i] : 0.f);
+        k_dst[i] = from_f<T>(wk ? a * r * wk[i] : a);
+    }
     const T* vr = v + (size_t)t * ld;
     T* v_dst = reinterpret_cast<T*>(page + v_off) + (size_t)at * v_cols;
-    for (int i = threadIdx.x; i < v_cols; i += blockDim.x) v_dst[i] = vr[i];
+    for (int i = threadIdx.x; i < v_cols; i += blockDim.x) v_dst[i] = from_f<T>(to_f(vr[i]) + (bv ? bv[i] : 0.f));
 }
 
 struct WindowGeom {

@@ -192,11 +192,8 @@ class HybridModel:
                 HD, GD, GV, HV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
                 parts = [p + "mix.q", p + "mix.k", p + "mix.v"] + ([p + "mix.g"] if m.gate else [])
                 w[p + "in"] = lin(*parts, shape=(HD + GD + GV + (HV if m.gate else 0), W))
-                if m.bias:
-                    b = torch.cat([get(p + f"mix.{k}.b").to(torch.float32) for k in "qkv"] + ([torch.zeros(HV)] if m.gate else []))
-                    if b.numel() != w[p + "in"].shape[0]:
-                        raise ValueError(f"{p}mix.[qkv].b: {b.numel()} entries, expected {HD + GD + GV}")
-                    w[p + "in.b"] = b.to(dev, T).contiguous()
+                if m.bias:          # added in float by the kernel that norms q and k and stores the cache (no bias pass over the GEMM's output)
+                    w[p + "in.b"] = torch.cat([f32(p + f"mix.{k}.b", (cols,)) for k, cols in (("q", HD), ("k", GD), ("v", GV))]).contiguous()
                 w[p + "o"] = lin(p + "mix.o", shape=(W, HV))
                 if m.qk_norm:
                     w[p + "q.norm"] = f32(p + "mix.q.norm", (HD,))
@@ -456,15 +453,15 @@ class HybridModel:
         return splits
 
     def window_mixer(self, i, h, c, run=None):
-        """Windowed attention of layer i: one stacked projection (q | k | v | gate) with its bias, RMS norm of q and k over their
-        whole projections + cache store, then attention over the window of cached keys with capped scores, distance penalty,
+        """Windowed attention of layer i: one stacked projection (q | k | v | gate), biases + RMS norm of q and k over their
+        whole projections + cache store in one kernel, then attention over the window of cached keys with capped scores, distance penalty,
         recombination of the heads' softmax weights, and the output gate.  Returns [n, heads * vdim] (T)."""
         r = i if run is None else run
         m, w, lib, dev, T, n = self.spec.layers[i].mixer, self.w, self.lib, self.device, self.T, c.n
         p = f"l{i}."
         HD, GD, GV, HV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
         with self.timed("gemm in"):
-            proj = torch.addmm(w[p + "in.b"], h, w[p + "in"].t()) if m.bias else self._linear(h, w[p + "in"])
+            proj = self._linear(h, w[p + "in"])
         ld, es, base = proj.stride(0), proj.element_size(), proj.data_ptr()
         f32 = dict(dtype=torch.float32, device=dev)
         a = H.WindowArgs()
@@ -472,6 +469,8 @@ class HybridModel:
         a.splits = self.window_splits(n, m.window, c.max_pos)
         a.scale, a.softcap, a.eps = m.scale, m.softcap, self.spec.norm_eps
         a.q, a.k, a.v, a.ld = base, base + es * HD, base + es * (HD + GD), ld
+        if m.bias:
+            a.bias = w[p + "in.b"].data_ptr()
         if m.qk_norm:
             a.q_norm, a.k_norm = w[p + "q.norm"].data_ptr(), w[p + "k.norm"].data_ptr()
         qn = torch.empty(n, HD, **f32)

@@ -246,6 +246,9 @@ class EmulatedHybridLib:
         assert a.dtype == F32
         H, G, D, V = a.heads, a.kv_heads, a.dim, a.vdim
         q, k, v = _rows(a.q, a.n, a.ld, H * D), _rows(a.k, a.n, a.ld, G * D), _rows(a.v, a.n, a.ld, G * V)
+        if a.bias:
+            b = _f(a.bias, (H + G) * D + G * V)
+            q, k, v = q + b[:H * D], k + b[H * D:(H + G) * D], v + b[(H + G) * D:]
         _f(a.qn, a.n, H * D)[:] = _unit(q, a.eps) * _f(a.q_norm, H * D) if a.q_norm else q
         kn = _unit(k, a.eps) * _f(a.k_norm, G * D) if a.k_norm else k
         seqs, poss = _i(a.tok_seq, a.n), _i(a.tok_pos, a.n)
