@@ -252,5 +252,35 @@ def residual_norm_and_both_convolutions(make, tol):
         _close(torch.cat(got), want, tol, f"input of sublayer {sub}")
 
 
-ALL = [whole_prompt, layer_by_layer, prefill_then_decode, token_by_token, portions, unequal_batch, reuse_of_pages_and_slots, other_sizes,
+def feed_forward_alone(make, tol):
+    """down(relu(up h)^2) over rows with negative and positive pre-activations."""
+    cfg = BC.config(loop=None)
+    w = BC.random_tensors(cfg, seed=33)
+    eng = make(cfg, w)
+    model = eng.model
+    h = torch.randn(37, cfg["width"], generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).float()
+    want = B.squared_relu_ff(h.double(), {"up": w["l0.mlp.up"].double(), "down": w["l0.mlp.down"].double()})
+    got = model.dense_mlp(0, h.to(model.device, model.T).contiguous()).float().cpu()
+    _close(got, want, tol, "feed-forward")
+
+
+def embedding_with_positions_and_pass_vectors(make, tol):
+    """The stream after the first run depends on the scaled embedding, the position's vector (a request that starts at position
+    0 against the same tokens fed later at other positions) and the vector of the first pass of a loop that starts at layer 0."""
+    cfg = BC.config(layers=[dict(BC.attention(window=4), mlp=None)], loop=(0, 1, 3))
+    w = BC.random_tensors(cfg, seed=34)
+    toks = BC.prompts_for(cfg, {"a": 6})["a"]
+    P = {"a": toks + toks}                                                   # the same six tokens at positions 0..5 and 6..11
+    eng = make(cfg, w)
+    eng.layer_trace = []
+    got = BC.replay(eng, P, [[("a", 6)], [("a", 6)]])
+    want = []
+    _check(got["a"], BC.oracle_logits(cfg, w, P["a"], trace=want), tol, "repeated tokens")
+    first, second = eng.layer_trace[0].double().cpu(), eng.layer_trace[3].double().cpu()       # run 0 of the first and of the second step
+    for g, x in ((first, want[0][:6]), (second, want[0][6:])):
+        assert float((g - x).abs().max() / x.abs().max()) <= tol
+    assert float((first - second).abs().max()) > 0.1                         # positions matter
+
+
+ALL = [feed_forward_alone, embedding_with_positions_and_pass_vectors, whole_prompt, layer_by_layer, prefill_then_decode, token_by_token, portions, unequal_batch, reuse_of_pages_and_slots, other_sizes,
        wider_sizes, greedy_generation, marked_keys_at_window_and_page_edges, residual_norm_and_both_convolutions]
