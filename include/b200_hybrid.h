@@ -17,59 +17,6 @@
 #define B200H_API extern "C" __attribute__((visibility("default")))
 #else
 #define B200H_API
-/* ---- pre-norm blocks: learned positions, residual add + RMS norm, windowed attention with grouped key/value heads ---- */
-
-/* x[t] += table[idx ? idx[t] : fixed] (x float [n, width], table T [rows, width], idx int [n] or NULL). */
-B200H_API int b200h_add_rows(void* x, const void* table, const void* idx, int fixed, int n, int width, int dtype, void* stream);
-
-/* x[t] += m[t] + extra (m T [n, width] or NULL, extra T [width] or NULL); then, if h is given, h[t] = x[t] / rms(x[t]) * w
- * (float [n, width]; w float [width] holds the full factor, i.e. one plus the stored deviation where a design stores that). */
-B200H_API int b200h_residual_norm(void* x, const void* m, const void* extra, const void* w, int n, int width, float eps, void* h,
-                                  int dtype, void* stream);
-
-/* x <- relu(x)^2 in place (T, `count` elements). */
-B200H_API int b200h_relu2(void* x, int64_t count, int dtype, void* stream);
-
-/* One layer of softmax attention over a sliding window of a paged key/value cache, for one step.
- * Query head h reads key/value head h / (heads / kv_heads).  For the query at position i and a key at position j,
- * max(0, i - window + 1) <= j <= i (window 0: every j <= i):
- *   s = scale * (q . k);  s <- softcap * tanh(s / softcap) if softcap > 0;  s <- s - r1[h] * ln(1 + r2[h] * (i - j)) if r1;
- *   weight = softmax over j;  weight_h <- sum_g talk[h, g] * weight_g if talk;  out_h = sum_j weight_h(j) * v_j;
- *   y = out * sigmoid(gate) if gate.
- * Cache entry of a position inside its page (page address + layer_off): the normed key as T at [pos % block_len][kv_heads * dim],
- * and, v_off bytes further, the value as T at [pos % block_len][kv_heads * vdim]. */
-typedef struct b200h_window_args {
-    int n, heads, kv_heads, dim, vdim, block_len, window, splits;
-    float scale, softcap, eps;
-    const void* q;           /* T [n, ld]: heads * dim columns */
-    const void* k;           /* T [n, ld]: kv_heads * dim columns */
-    const void* v;           /* T [n, ld]: kv_heads * vdim columns */
-    int64_t ld;
-    const void* bias;        /* float [heads * dim + kv_heads * dim + kv_heads * vdim] or NULL: added to q | k | v before anything else */
-    const void* q_norm;      /* float [heads * dim] or NULL: RMS norm over the whole query projection */
-    const void* k_norm;      /* float [kv_heads * dim] or NULL */
-    void* qn;                /* float [n, heads * dim]: out of b200h_window_prep */
-    const void* r1;          /* float [heads] or NULL */
-    const void* r2;          /* float [heads] */
-    const void* talk;        /* float [heads, heads] or NULL */
-    const void* gate;        /* T [n, ld_gate] or NULL */
-    int64_t ld_gate;
-    void* ml;                /* float [n, heads, splits, 2] scratch */
-    void* o_part;            /* float [n, splits, heads * vdim] scratch */
-    void* y;                 /* T [n, heads * vdim]: out of b200h_window_attention */
-    const void* tok_seq;     /* int [n] */
-    const void* tok_pos;     /* int [n] */
-    const void* block_ptrs;  /* int64: page addresses, entry s's pages from cu_blocks[s] */
-    const void* cu_blocks;   /* int [batch + 1] */
-    int64_t layer_off, v_off;
-    int dtype;
-    void* stream;
-} b200h_window_args;
-/* Bias, norm of query and key, cache store of key and value (fills qn). */
-B200H_API int b200h_window_prep(const b200h_window_args* args);
-/* Attention of the step's rows over the cache (fills y); the step's own rows must have been stored by b200h_window_prep. */
-B200H_API int b200h_window_attention(const b200h_window_args* args);
-
 #endif
 
 #define B200H_BF16 1
@@ -229,6 +176,8 @@ typedef struct b200h_window_args {
     int64_t ld_gate;
     void* ml;                /* float [n, heads, splits, 2] scratch */
     void* o_part;            /* float [n, splits, heads * vdim] scratch */
+    void* scores;            /* float [n, heads, score_ld] scratch: a row's scores, indexed by key position - the row's first visible key */
+    int64_t score_ld;        /* >= the most keys a row of the step sees: min(window, largest position + 1), all positions when window is 0 */
     void* y;                 /* T [n, heads * vdim]: out of b200h_window_attention */
     const void* tok_seq;     /* int [n] */
     const void* tok_pos;     /* int [n] */

@@ -45,7 +45,7 @@ class WindowArgs(C.Structure):
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("ld", C.c_int64),
         ("bias", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("qn", C.c_void_p),
         ("r1", C.c_void_p), ("r2", C.c_void_p), ("talk", C.c_void_p), ("gate", C.c_void_p), ("ld_gate", C.c_int64),
-        ("ml", C.c_void_p), ("o_part", C.c_void_p), ("y", C.c_void_p),
+        ("ml", C.c_void_p), ("o_part", C.c_void_p), ("scores", C.c_void_p), ("score_ld", C.c_int64), ("y", C.c_void_p),
         ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("block_ptrs", C.c_void_p), ("cu_blocks", C.c_void_p),
         ("layer_off", C.c_int64), ("v_off", C.c_int64), ("dtype", C.c_int), ("stream", C.c_void_p),
     ]

@@ -1026,8 +1026,8 @@ static size_t window_pv_smem(const b200h_window_args* a, int rows, int tile)
 {
     const size_t H = a->heads, rh = (size_t)rows * H;
     auto pad4 = [](size_t v) { return (v + 3) & ~(size_t)3; };
-    return (size_t)2 * tile * sizeof(char*) +
-           sizeof(float) * (pad4(rh * a->dim) + 2 * pad4(rh) + (a->talk ? pad4(H * H) : 0) + (size_t)(a->talk ? 2 : 1) * rh * tile + rh * a->vdim);
+    return (size_t)tile * sizeof(char*) +
+           sizeof(float) * (2 * pad4(rh) + (a->talk ? pad4(H * H) : 0) + (size_t)(a->talk ? 2 : 1) * rh * tile + rh * a->vdim);
 }
 
 struct WindowLaunch {
@@ -1041,23 +1041,21 @@ static void launch_window_kernels(const b200h_window_args* a, const WindowGeom& 
     if (l.stats_smem > 48 * 1024)
         cudaFuncSetAttribute(window_stats_kernel<T, VEC, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)l.stats_smem);
     if (l.pv_smem > 48 * 1024)
-        cudaFuncSetAttribute(window_pv_kernel<T, VEC, CW, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)l.pv_smem);
+        cudaFuncSetAttribute(window_pv_kernel<T, CW, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)l.pv_smem);
     window_stats_kernel<T, VEC, NP><<<dim3(l.blocks, a->kv_heads, a->splits), l.stats_threads, l.stats_smem, st>>>((const float*)a->qn, g,
                                                                                                                    (float*)a->ml);
-    window_pv_kernel<T, VEC, CW, NP><<<dim3(l.blocks, a->splits), 256, l.pv_smem, st>>>((const float*)a->qn, g, (const float*)a->ml,
-                                                                                        (float*)a->o_part);
+    window_pv_kernel<T, CW, NP><<<dim3(l.blocks, a->splits), 256, l.pv_smem, st>>>(g, (const float*)a->ml, (float*)a->o_part);
 }
 
 template <typename T, bool VEC, int CW>
 static int launch_window_attention(const b200h_window_args* a, WindowGeom g, cudaStream_t st)
 {
     const int H = a->heads, rep = H / a->kv_heads;
-    // Rows per block: four for prompt portions (one key range per row), one when the keys of a row are cut into ranges; keys per
-    // tile of pass 2: about one (key, key/value head) pair per thread.  Both shrink until a block fits half an SM's shared memory.
+    // Rows per block: four for prompt portions (one key range per row), one when the keys of a row are cut into ranges; 64 keys per
+    // tile of pass 2.  Both shrink until a block fits half an SM's shared memory.
     const size_t budget = 100 * 1024;
     g.rows = (a->splits == 1 && a->n >= 4) ? 4 : 1;
-    g.tile = (256 / a->kv_heads) & ~3;
-    g.tile = g.tile < 32 ? 32 : (g.tile > 128 ? 128 : g.tile);
+    g.tile = 64;
     while (window_pv_smem(a, g.rows, g.tile) > budget && g.tile > 32) g.tile /= 2;
     while (window_pv_smem(a, g.rows, g.tile) > budget && g.rows > 1) g.rows /= 2;
     WindowLaunch l;
@@ -1082,6 +1080,7 @@ B200H_API int b200h_window_attention(const b200h_window_args* a)
 {
     const char* why = "";
     if (!window_args_ok(a, &why)) return fail(B200H_ERR_INVALID_ARG, why);
+    if (!a->scores || a->score_ld < 1) return fail(B200H_ERR_INVALID_ARG, "window_attention: no score scratch");
     if (!a->ml || !a->o_part || !a->y || a->splits < 1 || a->splits > 65535 || a->kv_heads > 65535 || (a->r1 && !a->r2))
         return fail(B200H_ERR_INVALID_ARG, "window_attention: bad arguments");
     if (a->n == 0) return 0;
@@ -1093,6 +1092,7 @@ B200H_API int b200h_window_attention(const b200h_window_args* a)
     g.tok_seq = (const int*)a->tok_seq; g.tok_pos = (const int*)a->tok_pos;
     g.block_ptrs = (const int64_t*)a->block_ptrs; g.cu_blocks = (const int*)a->cu_blocks;
     g.layer_off = a->layer_off; g.v_off = a->v_off;
+    g.scores = (float*)a->scores; g.score_ld = (int)a->score_ld;
     cudaStream_t st = (cudaStream_t)a->stream;
     const size_t esize = a->dtype == B200H_F32 ? 4 : 2;
     // 16-byte key reads / four value columns per read where sizes and offsets keep every read aligned

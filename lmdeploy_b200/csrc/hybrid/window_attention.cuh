@@ -9,9 +9,9 @@
 // Attention runs in two passes over a row's visible keys [max(0, pos - window + 1), pos], both cut into `splits` equal key
 // ranges so that a step of few rows still fills the SMs:
 //   pass 1 (window_stats_kernel, one block per row block, key/value head and range): scores of the heads that share the key/value
-//          head, their running maximum and denominator;
+//          head, written to a scratch [row, head, key - first visible key], and their running maximum and denominator;
 //   pass 2 (window_pv_kernel, one block per row block and range): the ranges' (maximum, denominator) pairs are merged per head, the
-//          scores are computed again for ALL heads of the row, turned into final softmax weights, recombined across heads
+//          scores of ALL heads of the row are read back, turned into final softmax weights, recombined across heads
 //          (weight'_h = sum_g talk[h, g] weight_g -- this couples every head of a row, hence one block for all of them) and
 //          applied to the values of each head's own key/value head;
 //   window_out_kernel sums the ranges' partial outputs, applies sigmoid(gate) and writes T.
@@ -121,7 +121,12 @@ struct WindowGeom {
     const int64_t* block_ptrs;
     const int* cu_blocks;
     int64_t layer_off, v_off;
+    float* scores;            // [rows of the step, heads, score_ld]: score of a row's key j at index j - (the row's first visible key)
+    int score_ld;
 };
+
+// first visible key of a row at position pos
+__device__ __forceinline__ int window_first(const WindowGeom& g, int pos) { return g.window > 0 ? max(0, pos - g.window + 1) : 0; }
 
 // The key range `z` of consecutive rows of one sequence at positions first .. last: [j0, j1).  Every row masks the keys of the
 // range that it does not see.
@@ -241,7 +246,11 @@ __global__ void __launch_bounds__(128) window_stats_kernel(const float* __restri
                 for (int u = 0; u < NP; ++u) {
                     if (u < cnt) {
                         const int r = (ub + u) / rep, hh = (ub + u) - r * rep;
-                        if (window_sees(g, pos + r, j)) merge_ml(m[u], l[u], window_score(g, acc[u], c * rep + hh, pos + r - j), 1.0f);
+                        if (window_sees(g, pos + r, j)) {
+                            const float sc = window_score(g, acc[u], c * rep + hh, pos + r - j);
+                            g.scores[((size_t)(ta + r) * H + c * rep + hh) * g.score_ld + (j - window_first(g, pos + r))] = sc;
+                            merge_ml(m[u], l[u], sc, 1.0f);
+                        }
                     }
                 }
             }
@@ -290,22 +299,19 @@ template <> __device__ __forceinline__ void load_cols<bf16, 4>(const bf16* __res
 
 __device__ __forceinline__ int pad4(int v) { return (v + 3) & ~3; }
 
-// Pass 2.  grid (row blocks, splits), 256 threads.  Shared memory: the tile's key and value row addresses [2][tile], then floats
-// qs [kv_heads][rows * rep][dim] | mx [rows * heads] | linv [rows * heads] | talk [heads][heads] | p [rows * heads][tile] |
-// p2 [rows * heads][tile] | o [rows * heads][vdim] (every part padded to a multiple of four floats).
-// CW: value columns per thread and walk (4: 8- or 16-byte reads of the values).  NP: (row, head) pairs per walk over a key or a
-// value -- 2 for a step of single tokens with two heads per key/value head, which keeps registers low and more blocks resident.
-template <typename T, bool VEC, int CW, int NP>
-__global__ void __launch_bounds__(256) window_pv_kernel(const float* __restrict__ qn, WindowGeom g, const float* __restrict__ ml,
-                                                        float* __restrict__ o_part)
+// Pass 2.  grid (row blocks, splits), 256 threads.  Shared memory: the tile's value row addresses [tile], then floats
+// mx [rows * heads] | linv [rows * heads] | talk [heads][heads] | p [rows * heads][tile] | p2 [rows * heads][tile] |
+// o [rows * heads][vdim] (every part padded to a multiple of four floats).
+// CW: value columns per thread and walk (4: 8- or 16-byte reads of the values).  NP: (row, head) pairs per walk over a value -- 2 for
+// a step of single tokens with two heads per key/value head, which keeps registers low and more blocks resident.
+template <typename T, int CW, int NP>
+__global__ void __launch_bounds__(256) window_pv_kernel(WindowGeom g, const float* __restrict__ ml, float* __restrict__ o_part)
 {
     extern __shared__ __align__(16) unsigned char win_raw[];
     const int z = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
-    const int H = g.heads, G = g.kv_heads, rep = H / G, D = g.dim, V = g.vdim, KT = g.tile, maxpairs = g.rows * rep;
-    const char** krow = reinterpret_cast<const char**>(win_raw);
-    const char** vrow = krow + KT;
-    float* qs = reinterpret_cast<float*>(win_raw + (size_t)2 * KT * sizeof(char*));
-    float* mx = qs + pad4(g.rows * H * D);
+    const int H = g.heads, G = g.kv_heads, rep = H / G, V = g.vdim, KT = g.tile;
+    const char** vrow = reinterpret_cast<const char**>(win_raw);
+    float* mx = reinterpret_cast<float*>(win_raw + (size_t)KT * sizeof(char*));
     float* linv = mx + pad4(g.rows * H);
     float* talk = linv + pad4(g.rows * H);
     float* p = talk + (g.talk ? pad4(H * H) : 0);
@@ -314,17 +320,13 @@ __global__ void __launch_bounds__(256) window_pv_kernel(const float* __restrict_
     if (g.talk)
         for (int i = tid; i < H * H; i += nt) talk[i] = g.talk[i];
     const int t0 = blockIdx.x * g.rows, t1 = min(g.n, t0 + g.rows);
-    const size_t k_row = (size_t)G * D * sizeof(T), v_row = (size_t)G * V * sizeof(T);
+    const size_t v_row = (size_t)G * V * sizeof(T);
     for (int ta = t0; ta < t1;) {
         const int s = g.tok_seq[ta];
         int tb = ta + 1;
         while (tb < t1 && g.tok_seq[tb] == s) ++tb;
         const int nr = tb - ta, pos = g.tok_pos[ta], pairs = nr * rep;
         __syncthreads();
-        for (int i = tid; i < nr * H * D; i += nt) {
-            const int rh = i / D, d = i - rh * D, r = rh / H, h = rh - r * H, c = h / rep, hh = h - c * rep;
-            qs[((size_t)c * maxpairs + r * rep + hh) * D + d] = qn[(size_t)ta * H * D + i];
-        }
         for (int i = tid; i < nr * H * V; i += nt) o[i] = 0.f;
         for (int i = tid; i < nr * H; i += nt) {
             const float* src = ml + ((size_t)ta * H + i) * g.splits * 2;
@@ -338,35 +340,19 @@ __global__ void __launch_bounds__(256) window_pv_kernel(const float* __restrict_
         const int64_t* pages = g.block_ptrs + g.cu_blocks[s];
         for (int jt = j0; jt < j1; jt += KT) {
             const int kt = min(KT, j1 - jt), kt4 = pad4(kt);
-            __syncthreads();                      // the previous tile's readers are done; qs / mx / o of this segment are in place
+            __syncthreads();                      // the previous tile's readers are done; mx / o of this segment are in place
             for (int jj = tid; jj < kt; jj += nt) {
                 const int j = jt + jj;
-                const char* page = window_page(g, pages, j);
-                krow[jj] = page + (size_t)(j % g.block_len) * k_row;
-                vrow[jj] = page + g.v_off + (size_t)(j % g.block_len) * v_row;
+                vrow[jj] = window_page(g, pages, j) + g.v_off + (size_t)(j % g.block_len) * v_row;
             }
-            for (int i = tid; i < nr * H * (kt4 - kt); i += nt) {          // weights of the keys that pad the tile to four
-                const int rh = i / (kt4 - kt);
-                p[(size_t)rh * KT + kt + (i - rh * (kt4 - kt))] = 0.f;
-            }
-            __syncthreads();
-            // final softmax weights of every (row, head) for the tile's keys: one (key, key/value head) pair per thread
-            for (int item = tid; item < kt * G; item += nt) {
-                const int c = item / kt, jj = item - c * kt, j = jt + jj;
-                const T* key = reinterpret_cast<const T*>(krow[jj]) + (size_t)c * D;
-                for (int ub = 0; ub < pairs; ub += NP) {
-                    const int cnt = min(NP, pairs - ub);
-                    float acc[NP];
-                    key_dots<T, VEC, NP>(key, qs + ((size_t)c * maxpairs + ub) * D, D, cnt, acc);
-#pragma unroll
-                    for (int u = 0; u < NP; ++u) {
-                        if (u < cnt) {
-                            const int r = (ub + u) / rep, h = c * rep + (ub + u) - r * rep, rh = r * H + h;
-                            p[(size_t)rh * KT + jj] =
-                                window_sees(g, pos + r, j) ? expf(window_score(g, acc[u], h, pos + r - j) - mx[rh]) * linv[rh] : 0.f;
-                        }
-                    }
-                }
+            // final softmax weights of every (row, head) for the tile's keys (zero for a key the row does not see and for the
+            // keys that pad the tile to a multiple of four), from the scores pass 1 left
+            for (int item = tid; item < nr * H * kt4; item += nt) {
+                const int rh = item / kt4, jj = item - rh * kt4, j = jt + jj, r = rh / H;
+                float w = 0.f;
+                if (jj < kt && window_sees(g, pos + r, j))
+                    w = expf(g.scores[((size_t)ta * H + rh) * g.score_ld + (j - window_first(g, pos + r))] - mx[rh]) * linv[rh];
+                p[(size_t)rh * KT + jj] = w;
             }
             __syncthreads();
             if (g.talk) {

@@ -117,6 +117,7 @@ class HybridModel:
         self.weight_bytes = 0
         self.grouped_experts_rows = 24    # steps that give an expert this many rows on average run the experts as grouped GEMMs
         self.attention_warps = 148 * 16   # warps a latent-attention launch aims for (one per row, head and key range)
+        self.window_scratch_bytes = 256 << 20    # most bytes of scores a windowed-attention launch leaves between its two passes
         self.events = None          # a list while profiling: (operator, start event, end event) of every timed region
         if spec.dtype == "f32":
             # float32 serving means true 32-bit products: no TF32, no reduced-precision accumulation
@@ -452,6 +453,14 @@ class HybridModel:
             splits *= 2
         return splits
 
+    @staticmethod
+    def window_score_ld(window, max_pos):
+        """Row length of the score scratch: the keys a row of the step can see, in steps of 256 (a captured decode step is valid
+        until the context outgrows it: the engine keys its graphs on this) and never more than the window."""
+        keys = min(window, max_pos + 1) if window else max_pos + 1
+        ld = (keys + 255) // 256 * 256
+        return min(ld, (window + 3) // 4 * 4) if window else ld
+
     def window_mixer(self, i, h, c, run=None):
         """Windowed attention of layer i: one stacked projection (q | k | v | gate), biases + RMS norm of q and k over their
         whole projections + cache store in one kernel, then attention over the window of cached keys with capped scores, distance penalty,
@@ -481,17 +490,30 @@ class HybridModel:
             a.talk = w[p + "talk"].data_ptr()
         if m.gate:
             a.gate, a.ld_gate = base + es * (HD + GD + GV), ld
-        ml = torch.empty(n, m.heads, a.splits, 2, **f32)
-        o_part = torch.empty(n, a.splits, HV, **f32)
         y = torch.empty(n, HV, dtype=T, device=dev)
-        a.ml, a.o_part, a.y = ml.data_ptr(), o_part.data_ptr(), y.data_ptr()
         a.tok_seq, a.tok_pos = c.tok_seq.data_ptr(), c.tok_pos.data_ptr()
         a.block_ptrs, a.cu_blocks = c.block_ptrs.data_ptr(), c.cu_blocks.data_ptr()
         a.layer_off, a.v_off, a.dtype, a.stream = self.cache_off[r], self.v_off[r], self.dt, self._stream()
         with self.timed("qk norm + cache store"):
             H.check(lib.b200h_window_prep(C.byref(a)), "window_prep")
+        # pass 1 leaves every row's scores in a scratch [rows, heads, keys a row can see] for pass 2; the step's rows go through
+        # the two passes in chunks that keep the scratch within `window_scratch_bytes`
+        a.score_ld = self.window_score_ld(m.window, c.max_pos)
+        chunk = max(4, self.window_scratch_bytes // (4 * m.heads * a.score_ld) // 4 * 4)
+        rows = min(n, chunk)
+        scores = torch.empty(rows, m.heads, a.score_ld, **f32)
+        ml = torch.empty(rows, m.heads, a.splits, 2, **f32)
+        o_part = torch.empty(rows, a.splits, HV, **f32)
+        a.scores, a.ml, a.o_part = scores.data_ptr(), ml.data_ptr(), o_part.data_ptr()
+        gate = a.gate
         with self.timed("windowed attention"):
-            H.check(lib.b200h_window_attention(C.byref(a)), "window_attention")
+            for at in range(0, n, chunk):
+                a.n = min(chunk, n - at)
+                a.qn, a.y = qn.data_ptr() + 4 * at * HD, y.data_ptr() + es * at * HV
+                a.tok_seq, a.tok_pos = c.tok_seq.data_ptr() + 4 * at, c.tok_pos.data_ptr() + 4 * at
+                if m.gate:
+                    a.gate = gate + es * at * ld
+                H.check(lib.b200h_window_attention(C.byref(a)), "window_attention")
         return y
 
     def dense_mlp(self, i, h):
@@ -533,7 +555,7 @@ class HybridModel:
             if l.mixer.kind == "latent_attention":
                 key.append(self.attention_splits(n, l.mixer.heads, max_pos))
             elif l.mixer.kind == "window_attention":
-                key.append(self.window_splits(n, l.mixer.window, max_pos))
+                key.append((self.window_splits(n, l.mixer.window, max_pos), self.window_score_ld(l.mixer.window, max_pos)))
         return tuple(key)
 
     def conv_input(self, i, x, c, run=None, sub=1):

@@ -282,5 +282,18 @@ def embedding_with_positions_and_pass_vectors(make, tol):
     assert float((first - second).abs().max()) > 0.1                         # positions matter
 
 
-ALL = [feed_forward_alone, embedding_with_positions_and_pass_vectors, whole_prompt, layer_by_layer, prefill_then_decode, token_by_token, portions, unequal_batch, reuse_of_pages_and_slots, other_sizes,
+def score_scratch_in_row_chunks(make, tol):
+    """The rows of a step pass through the attention in chunks when the scratch between its two passes is bounded: chunks of 4
+    rows here, cut inside sequences and between them."""
+    cfg = BC.config()
+    w = BC.random_tensors(cfg, seed=35)
+    P = BC.prompts_for(cfg, {"a": 93, "b": 21, "c": 3})
+    eng = make(cfg, w)
+    eng.model.window_scratch_bytes = 1
+    got = BC.replay(eng, P, [[("a", 50), ("b", 21), ("c", 2)], [("a", 43), ("c", 1)]])
+    for k in P:
+        _check(got[k], BC.oracle_logits(cfg, w, P[k]), tol, f"row chunks {k}")
+
+
+ALL = [feed_forward_alone, score_scratch_in_row_chunks, embedding_with_positions_and_pass_vectors, whole_prompt, layer_by_layer, prefill_then_decode, token_by_token, portions, unequal_batch, reuse_of_pages_and_slots, other_sizes,
        wider_sizes, greedy_generation, marked_keys_at_window_and_page_edges, residual_norm_and_both_convolutions]
