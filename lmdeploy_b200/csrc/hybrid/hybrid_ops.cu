@@ -1059,14 +1059,14 @@ static int launch_window_attention(const b200h_window_args* a, WindowGeom g, cud
     while (window_pv_smem(a, g.rows, g.tile) > budget && g.tile > 32) g.tile /= 2;
     while (window_pv_smem(a, g.rows, g.tile) > budget && g.rows > 1) g.rows /= 2;
     WindowLaunch l;
-    l.stats_smem = (size_t)g.rows * rep * a->dim * sizeof(float);
+    // pass 1: a thread per key of the range, at most 128
+    const int keys = a->window > 0 ? a->window + g.rows - 1 : 1 << 30, per = (keys + a->splits - 1) / a->splits;
+    l.stats_threads = per <= 32 ? 32 : (per <= 64 ? 64 : 128);
+    l.stats_smem = (size_t)g.rows * rep * a->dim * sizeof(float) + (VEC ? (size_t)l.stats_threads * (a->dim * sizeof(T) + 16) : 0);
     l.pv_smem = window_pv_smem(a, g.rows, g.tile);
     if (l.stats_smem > 200 * 1024 || l.pv_smem > 200 * 1024)
         return fail(B200H_ERR_UNSUPPORTED, "window_attention: heads * (dim + vdim + heads) floats exceed an SM's shared memory");
     l.blocks = (a->n + g.rows - 1) / g.rows;
-    // pass 1: a thread per key of the range, at most 128
-    const int keys = a->window > 0 ? a->window + g.rows - 1 : 1 << 30, per = (keys + a->splits - 1) / a->splits;
-    l.stats_threads = per <= 32 ? 32 : (per <= 64 ? 64 : 128);
     const int pairs = g.rows * rep;              // (row, head) pairs that share a key: walked NP at a time
     if (pairs <= 2) launch_window_kernels<T, VEC, CW, 2>(a, g, l, st);
     else if (pairs <= 4) launch_window_kernels<T, VEC, CW, 4>(a, g, l, st);

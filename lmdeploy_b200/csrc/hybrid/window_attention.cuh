@@ -218,6 +218,9 @@ __global__ void __launch_bounds__(128) window_stats_kernel(const float* __restri
     const int H = g.heads, D = g.dim, rep = H / g.kv_heads;
     const int t0 = blockIdx.x * g.rows, t1 = min(g.n, t0 + g.rows);
     float* qs = win_smem;                                                    // [rows * rep][dim]
+    // VEC: one key row per thread after the queries, rows 16 bytes apart from a multiple of 128 so that the 16-byte reads of a
+    // quarter warp fall into different banks
+    char* stage = reinterpret_cast<char*>(win_smem + (size_t)g.rows * rep * D) + (size_t)tid * (D * sizeof(T) + 16);
     const size_t k_row = (size_t)g.kv_heads * D;
     for (int ta = t0; ta < t1;) {
         const int s = g.tok_seq[ta];
@@ -240,6 +243,16 @@ __global__ void __launch_bounds__(128) window_stats_kernel(const float* __restri
             for (int u = 0; u < NP; ++u) { m[u] = -1e30f; l[u] = 0.f; }
             for (int j = j0 + tid; j < j1; j += blockDim.x) {
                 const T* key = reinterpret_cast<const T*>(window_page(g, pages, j)) + (size_t)(j % g.block_len) * k_row + (size_t)c * D;
+                if (VEC) {
+                    // the thread's key travels to its own row of shared memory by asynchronous 16-byte copies: all of them are in
+                    // flight at once and hold no registers; only the issuing thread reads the row, so its own wait suffices
+                    const unsigned dst = (unsigned)__cvta_generic_to_shared(stage);
+                    for (int b = 0; b < D * (int)sizeof(T); b += 16)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + b), "l"(reinterpret_cast<const char*>(key) + b) : "memory");
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    key = reinterpret_cast<const T*>(stage);
+                }
                 float acc[NP];
                 key_dots<T, VEC, NP>(key, qs + (size_t)ub * D, D, cnt, acc);
 #pragma unroll
