@@ -180,7 +180,7 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", default="c2", choices=list(CONFIGS))
     ap.add_argument("--hybrid", default=None, choices=list(HYBRID_SIZES),
-                    help="instead of the default workload: prefill and decode tokens/s of a Gulozen hybrid decoder of this size "
+                    help="instead of the default workload: prefill and decode tokens/s of a hybrid decoder of this size (--hybrid-design) "
                          "beside the dense decoder of equal size, both through the engine (random weights)")
     ap.add_argument("--hybrid-design", default="gulozen", choices=["gulozen", "bodopel"],
                     help="which hybrid design --hybrid builds: Gulozen (latent / decayed linear attention, routed experts) or Bodopel "

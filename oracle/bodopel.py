@@ -1,7 +1,7 @@
 """Plain, slow restatement of the Bodopel layer equations in torch on the CPU -- TEST INFRASTRUCTURE ONLY.
 
-One function per mechanism, written key by key and head by head (explicit loops over query position, key position and
-head, no paging, no batching, no tiling, no two-pass softmax): the opposite route from the product kernels in
+One function per mechanism, written row by row and head by head (explicit loops over query position and head, every visible
+key of a row at once; no paging, no batching, no tiling, no two-pass softmax, no key ranges): the opposite route from the product kernels in
 lmdeploy_b200/csrc/hybrid/hybrid_ops.cu, with which it shares no code.  `dt` is the dtype everything runs in (float64 by
 default).
 

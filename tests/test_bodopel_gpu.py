@@ -43,6 +43,22 @@ def test_key_ranges_of_a_short_step_agree_with_one_range():
     S._check(got["a"], BC.oracle_logits(cfg, w, P["a"]), 2e-5, "key ranges")
 
 
+def test_do_sample_through_the_engine_is_a_function_of_the_seed():
+    """Sampling requests run the framework's device sampling stage on this decoder's logits; a greedy request beside them is
+    not affected by the seed."""
+    from lmdeploy_b200.messages import GenerationConfig
+    from lmdeploy_b200.turbomind.engine import batched_generate
+    cfg = BC.config()
+    w = BC.random_tensors(cfg, seed=9)
+    P = BC.prompts_for(cfg, {"a": 9, "b": 20})
+    run = lambda seed: [list(s.generated) for s in batched_generate(
+        BC.build_engine(cfg, w, device="cuda", dtype="bf16"), [P["a"], P["b"]],
+        [GenerationConfig(max_new_tokens=12, ignore_eos=True, do_sample=True, top_k=20, temperature=1.5, random_seed=seed),
+         GenerationConfig(max_new_tokens=12, ignore_eos=True)])]
+    a, b, c = run(1), run(1), run(2)
+    assert a == b and a[0] != c[0] and a[1] == c[1]
+
+
 def test_graph_replay_generates_what_eager_launches_generate(monkeypatch):
     from lmdeploy_b200.messages import GenerationConfig
     from lmdeploy_b200.turbomind.engine import batched_generate
